@@ -1,0 +1,449 @@
+// Plan builder: turns upstream's three part-major index layouts into one destination-major
+// work list.
+//
+// Upstream runs one warp per *part* and adds every part's sum into its destination row with
+// atomics (reuse_conv_kernel.cu:230-285, 521-600, 879-953).  Here the same index tensors are
+// transposed once, on the host, into rows of entries: an entry < N names a feature row, an
+// entry >= N names the partial sum of reuse group (entry - N).  Rows longer than
+// kSegmentEdges are cut into segments whose sums are combined by a second small kernel in a
+// fixed order, so the result is deterministic.  Work items are ordered longest first so the
+// hardware block scheduler balances the power-law tail.
+#include <algorithm>
+#include <cstring>
+#include <memory>
+#include <numeric>
+
+#include "rof_internal.h"
+
+namespace rof {
+
+static thread_local std::string g_error = "";
+
+void set_error(const std::string& msg) { g_error = msg; }
+
+int cuda_fail(cudaError_t e, const char* what) {
+  set_error(std::string(what) + ": " + cudaGetErrorString(e));
+  return ROF_ERR_CUDA;
+}
+
+const std::string& last_error() { return g_error; }
+
+namespace {
+
+// Host view of an int32 index array that may live on the device.
+struct HostArray {
+  std::vector<int32_t> owned;
+  const int32_t* ptr = nullptr;
+  int64_t n = 0;
+  int fetch(const int32_t* src, int64_t count, int where, cudaStream_t stream, const char* name) {
+    n = count;
+    if (count < 0) { set_error(std::string(name) + ": negative length"); return ROF_ERR_BAD_ARGUMENT; }
+    if (count == 0) { ptr = nullptr; return ROF_OK; }
+    if (src == nullptr) { set_error(std::string(name) + ": null pointer"); return ROF_ERR_BAD_ARGUMENT; }
+    if (where == ROF_ON_HOST) { ptr = src; return ROF_OK; }
+    try { owned.resize((size_t)count); } catch (...) { set_error("out of host memory"); return ROF_ERR_NO_MEMORY; }
+    cudaError_t e = cudaMemcpyAsync(owned.data(), src, sizeof(int32_t) * (size_t)count, cudaMemcpyDeviceToHost, stream);
+    if (e != cudaSuccess) return cuda_fail(e, name);
+    ptr = owned.data();
+    return ROF_OK;
+  }
+};
+
+int bad_layout(const std::string& msg) {
+  set_error("bad layout: " + msg);
+  return ROF_ERR_BAD_LAYOUT;
+}
+
+int check_common(rof_plan** plan, int where, int num_nodes, int row_begin, int row_end) {
+  if (plan == nullptr) { set_error("plan: null output pointer"); return ROF_ERR_BAD_ARGUMENT; }
+  *plan = nullptr;
+  if (where != ROF_ON_HOST && where != ROF_ON_DEVICE) { set_error("where: unknown location"); return ROF_ERR_BAD_ARGUMENT; }
+  if (num_nodes < 0 || row_begin < 0 || row_end < row_begin || row_end > num_nodes) {
+    set_error("num_nodes / row range out of order");
+    return ROF_ERR_BAD_ARGUMENT;
+  }
+  return ROF_OK;
+}
+
+// pointers[count+1] must be non-decreasing and stay inside [0, limit]
+int check_pointers(const int32_t* p, int64_t count, int64_t limit, const char* name) {
+  if (count == 0) return ROF_OK;
+  for (int64_t i = 0; i <= count; ++i) {
+    if (p[i] < 0 || p[i] > limit) return bad_layout(std::string(name) + " leaves its index array");
+    if (i > 0 && p[i] < p[i - 1]) return bad_layout(std::string(name) + " is not non-decreasing");
+  }
+  return ROF_OK;
+}
+
+int check_ids(const int32_t* p, int64_t count, int64_t limit, const char* name) {
+  for (int64_t i = 0; i < count; ++i)
+    if (p[i] < 0 || p[i] >= limit) return bad_layout(std::string(name) + " holds an id outside [0, num_nodes)");
+  return ROF_OK;
+}
+
+int sync_if_device(int where, cudaStream_t stream) {
+  if (where != ROF_ON_DEVICE) return ROF_OK;
+  cudaError_t e = cudaStreamSynchronize(stream);
+  return e == cudaSuccess ? ROF_OK : cuda_fail(e, "copy of index tensors to the host");
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
+// finalize: row lists -> sorted work items -> device
+// ---------------------------------------------------------------------------------------
+int finalize_plan(const HostPlan& hp, rof_plan** out, cudaStream_t stream) {
+  const int rows = hp.row_end - hp.row_begin;
+  const int64_t entries = (int64_t)hp.col.size();
+  const int64_t gsrc = (int64_t)hp.group_col.size();
+  const int groups = (int)hp.group_ptr.size() - 1;
+  if (entries + gsrc >= (int64_t)INT32_MAX) {
+    set_error("more than 2^31-1 gather entries in one plan; shard the rows");
+    return ROF_ERR_BAD_ARGUMENT;
+  }
+
+  std::unique_ptr<rof_plan> p(new rof_plan());
+  cudaError_t e = cudaGetDevice(&p->device);
+  if (e != cudaSuccess) {
+    // No usable device: keep the plan on the host so that it can still be inspected with
+    // rof_plan_export(); rof_aggregate() refuses such a plan.
+    (void)cudaGetLastError();
+    p->device = -1;
+  }
+  p->num_nodes = hp.num_nodes;
+  p->row_begin = hp.row_begin;
+  p->row_end = hp.row_end;
+  p->num_groups = groups < 0 ? 0 : groups;
+  p->group_sources = gsrc;
+  p->gather_entries = entries;
+  p->original_edges = hp.original_edges;
+  for (int32_t c : hp.col) p->partial_entries += (c >= hp.num_nodes);
+
+  // rows ordered by length, longest first (stable: equal lengths keep ascending row id)
+  std::vector<int32_t> order((size_t)rows);
+  std::iota(order.begin(), order.end(), 0);
+  std::stable_sort(order.begin(), order.end(), [&](int32_t a, int32_t b) {
+    return (hp.row_ptr[a + 1] - hp.row_ptr[a]) > (hp.row_ptr[b + 1] - hp.row_ptr[b]);
+  });
+
+  std::vector<WorkItem> items;
+  std::vector<SplitRow> split;
+  items.reserve((size_t)rows + (size_t)(entries / kSegmentEdges) + 1);
+  int slots = 0;
+  for (int32_t r : order) {
+    const int64_t b = hp.row_ptr[r], en = hp.row_ptr[r + 1];
+    const int64_t len = en - b;
+    if (len <= kSegmentEdges) {
+      items.push_back(WorkItem{(int32_t)b, (int32_t)en, hp.row_begin + r, 0});
+    } else {
+      const int nseg = (int)((len + kSegmentEdges - 1) / kSegmentEdges);
+      split.push_back(SplitRow{hp.row_begin + r, slots, nseg, 0});
+      for (int s = 0; s < nseg; ++s) {
+        const int64_t sb = b + (int64_t)s * kSegmentEdges;
+        const int64_t se = std::min(en, sb + kSegmentEdges);
+        items.push_back(WorkItem{(int32_t)sb, (int32_t)se, -(slots + s) - 1, 0});
+      }
+      slots += nseg;
+    }
+  }
+  // full segments first, then everything else by length (split rows' short tails included)
+  std::stable_sort(items.begin(), items.end(),
+                   [](const WorkItem& a, const WorkItem& b) { return (a.end - a.begin) > (b.end - b.begin); });
+  p->num_items = (int)items.size();
+  p->num_split_rows = (int)split.size();
+  p->num_slots = slots;
+
+  std::vector<WorkItem> gitems((size_t)p->num_groups);
+  for (int g = 0; g < p->num_groups; ++g)
+    gitems[g] = WorkItem{(int32_t)(entries + hp.group_ptr[g]), (int32_t)(entries + hp.group_ptr[g + 1]), g, 0};
+
+  p->h_row_ptr = hp.row_ptr;
+  p->h_group_ptr = hp.group_ptr;
+  p->h_items = items;
+  p->h_split = split;
+  if (p->device < 0) {
+    p->h_col = hp.col;
+    p->h_col.insert(p->h_col.end(), hp.group_col.begin(), hp.group_col.end());
+    *out = p.release();
+    return ROF_OK;
+  }
+
+  auto upload = [&](void** dptr, const void* src, size_t bytes, const char* what) -> int {
+    *dptr = nullptr;
+    if (bytes == 0) return ROF_OK;
+    cudaError_t err = cudaMalloc(dptr, bytes);
+    if (err != cudaSuccess) return cuda_fail(err, what);
+    err = cudaMemcpyAsync(*dptr, src, bytes, cudaMemcpyHostToDevice, stream);
+    if (err != cudaSuccess) return cuda_fail(err, what);
+    return ROF_OK;
+  };
+  int rc = ROF_OK;
+  {
+    size_t bytes = sizeof(int32_t) * (size_t)(entries + gsrc);
+    if (bytes) {
+      e = cudaMalloc((void**)&p->d_col, bytes);
+      if (e != cudaSuccess) rc = cuda_fail(e, "cudaMalloc(col)");
+      if (rc == ROF_OK && entries) {
+        e = cudaMemcpyAsync(p->d_col, hp.col.data(), sizeof(int32_t) * (size_t)entries, cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) rc = cuda_fail(e, "upload col");
+      }
+      if (rc == ROF_OK && gsrc) {
+        e = cudaMemcpyAsync(p->d_col + entries, hp.group_col.data(), sizeof(int32_t) * (size_t)gsrc,
+                            cudaMemcpyHostToDevice, stream);
+        if (e != cudaSuccess) rc = cuda_fail(e, "upload group sources");
+      }
+    }
+  }
+  if (rc == ROF_OK) rc = upload((void**)&p->d_items, items.data(), sizeof(WorkItem) * items.size(), "upload work items");
+  if (rc == ROF_OK) rc = upload((void**)&p->d_group_items, gitems.data(), sizeof(WorkItem) * gitems.size(), "upload group items");
+  if (rc == ROF_OK) rc = upload((void**)&p->d_split, split.data(), sizeof(SplitRow) * split.size(), "upload split rows");
+  if (rc == ROF_OK) {
+    e = cudaStreamSynchronize(stream);  // the host vectors die at return
+    if (e != cudaSuccess) rc = cuda_fail(e, "plan upload");
+  }
+  if (rc != ROF_OK) {
+    rof_plan_destroy(p.release());
+    return rc;
+  }
+  *out = p.release();
+  return ROF_OK;
+}
+
+}  // namespace rof
+
+using namespace rof;
+
+extern "C" {
+
+int rof_plan_create_parts(rof_plan** plan, int where, int num_nodes, int row_begin, int row_end,
+                          const int32_t* column_index, int64_t num_column_index,
+                          const int32_t* part_pointers, const int32_t* part2Node, int num_parts,
+                          void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int rc = check_common(plan, where, num_nodes, row_begin, row_end);
+  if (rc) return rc;
+  if (num_parts < 0) { set_error("num_parts < 0"); return ROF_ERR_BAD_ARGUMENT; }
+  HostArray col, pp, p2n;
+  if ((rc = col.fetch(column_index, num_column_index, where, stream, "column_index"))) return rc;
+  if ((rc = pp.fetch(part_pointers, num_parts ? (int64_t)num_parts + 1 : 0, where, stream, "part_pointers"))) return rc;
+  if ((rc = p2n.fetch(part2Node, num_parts, where, stream, "part2Node"))) return rc;
+  if ((rc = sync_if_device(where, stream))) return rc;
+  if ((rc = check_pointers(pp.ptr, num_parts, num_column_index, "part_pointers"))) return rc;
+  if ((rc = check_ids(p2n.ptr, num_parts, num_nodes, "part2Node"))) return rc;
+  if ((rc = check_ids(col.ptr, num_column_index, num_nodes, "column_index"))) return rc;
+
+  HostPlan hp;
+  hp.num_nodes = num_nodes; hp.row_begin = row_begin; hp.row_end = row_end;
+  const int rows = row_end - row_begin;
+  try {
+    hp.row_ptr.assign((size_t)rows + 1, 0);
+    for (int p = 0; p < num_parts; ++p) {
+      int v = p2n.ptr[p];
+      if (v >= row_begin && v < row_end) hp.row_ptr[(size_t)(v - row_begin) + 1] += pp.ptr[p + 1] - pp.ptr[p];
+    }
+    for (int r = 0; r < rows; ++r) hp.row_ptr[r + 1] += hp.row_ptr[r];
+    hp.col.resize((size_t)hp.row_ptr[rows]);
+    std::vector<int64_t> pos(hp.row_ptr.begin(), hp.row_ptr.end() - 1);
+    for (int p = 0; p < num_parts; ++p) {
+      int v = p2n.ptr[p];
+      if (v < row_begin || v >= row_end) continue;
+      int64_t& w = pos[(size_t)(v - row_begin)];
+      for (int32_t k = pp.ptr[p]; k < pp.ptr[p + 1]; ++k) hp.col[(size_t)w++] = col.ptr[k];
+    }
+    hp.group_ptr.assign(1, 0);
+    hp.original_edges = hp.row_ptr[rows];
+  } catch (const std::bad_alloc&) {
+    set_error("out of host memory while building the plan");
+    return ROF_ERR_NO_MEMORY;
+  }
+  return finalize_plan(hp, plan, stream);
+}
+
+int rof_plan_create_v1(rof_plan** plan, int where, int num_nodes, int row_begin, int row_end,
+                       const int32_t* column_index, int64_t num_column_index,
+                       const int32_t* part_pointers, const int32_t* part2Node, int num_parts,
+                       const int32_t* part_cache_flagindex, const int32_t* part_pointers_cache,
+                       const int32_t* column_index_cache, int num_groups, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int rc = check_common(plan, where, num_nodes, row_begin, row_end);
+  if (rc) return rc;
+  if (num_parts < 0 || num_groups < 0) { set_error("num_parts / num_groups < 0"); return ROF_ERR_BAD_ARGUMENT; }
+  HostArray col, pp, p2n, flag, ppc, cic;
+  if ((rc = col.fetch(column_index, num_column_index, where, stream, "column_index"))) return rc;
+  if ((rc = pp.fetch(part_pointers, num_parts ? (int64_t)num_parts + 1 : 0, where, stream, "part_pointers"))) return rc;
+  if ((rc = p2n.fetch(part2Node, num_parts, where, stream, "part2Node"))) return rc;
+  if ((rc = flag.fetch(part_cache_flagindex, num_parts, where, stream, "part_cache_flagindex"))) return rc;
+  if ((rc = ppc.fetch(part_pointers_cache, num_groups ? (int64_t)num_groups + 1 : 0, where, stream, "part_pointers_cache"))) return rc;
+  if ((rc = sync_if_device(where, stream))) return rc;
+  int64_t n_cic = num_groups ? ppc.ptr[num_groups] : 0;
+  if (n_cic < 0) return bad_layout("part_pointers_cache ends below zero");
+  if ((rc = cic.fetch(column_index_cache, n_cic, where, stream, "column_index_cache"))) return rc;
+  if ((rc = sync_if_device(where, stream))) return rc;
+  if ((rc = check_pointers(pp.ptr, num_parts, num_column_index, "part_pointers"))) return rc;
+  if ((rc = check_pointers(ppc.ptr, num_groups, n_cic, "part_pointers_cache"))) return rc;
+  if ((rc = check_ids(p2n.ptr, num_parts, num_nodes, "part2Node"))) return rc;
+  if ((rc = check_ids(col.ptr, num_column_index, num_nodes, "column_index"))) return rc;
+  if ((rc = check_ids(cic.ptr, n_cic, num_nodes, "column_index_cache"))) return rc;
+  for (int p = 0; p < num_parts; ++p)
+    if (flag.ptr[p] < 0 || flag.ptr[p] > num_groups) return bad_layout("part_cache_flagindex names a group that does not exist");
+
+  HostPlan hp;
+  hp.num_nodes = num_nodes; hp.row_begin = row_begin; hp.row_end = row_end;
+  const int rows = row_end - row_begin;
+  try {
+    hp.row_ptr.assign((size_t)rows + 1, 0);
+    for (int p = 0; p < num_parts; ++p) {
+      int v = p2n.ptr[p];
+      if (v < row_begin || v >= row_end) continue;
+      hp.row_ptr[(size_t)(v - row_begin) + 1] += flag.ptr[p] > 0 ? 1 : pp.ptr[p + 1] - pp.ptr[p];
+      hp.original_edges += pp.ptr[p + 1] - pp.ptr[p];
+    }
+    for (int r = 0; r < rows; ++r) hp.row_ptr[r + 1] += hp.row_ptr[r];
+    hp.col.resize((size_t)hp.row_ptr[rows]);
+    std::vector<int64_t> pos(hp.row_ptr.begin(), hp.row_ptr.end() - 1);
+    for (int p = 0; p < num_parts; ++p) {
+      int v = p2n.ptr[p];
+      if (v < row_begin || v >= row_end) continue;
+      int64_t& w = pos[(size_t)(v - row_begin)];
+      if (flag.ptr[p] > 0) {
+        hp.col[(size_t)w++] = num_nodes + (flag.ptr[p] - 1);
+      } else {
+        for (int32_t k = pp.ptr[p]; k < pp.ptr[p + 1]; ++k) hp.col[(size_t)w++] = col.ptr[k];
+      }
+    }
+    // every group keeps its id: upstream's caching kernel fills all rows of the caller's
+    // part_result_cache (reuse_conv_kernel.cu:427-486), used or not
+    if (num_groups > 0) {
+      hp.group_ptr.assign(ppc.ptr, ppc.ptr + num_groups + 1);
+      hp.group_col.assign(cic.ptr, cic.ptr + n_cic);
+    } else {
+      hp.group_ptr.assign(1, 0);
+    }
+  } catch (const std::bad_alloc&) {
+    set_error("out of host memory while building the plan");
+    return ROF_ERR_NO_MEMORY;
+  }
+  return finalize_plan(hp, plan, stream);
+}
+
+int rof_plan_create_v2(rof_plan** plan, int where, int num_nodes, int row_begin, int row_end,
+                       const int32_t* uniqpart_column_index, int64_t num_column_index,
+                       const int32_t* uniqpart_pointers, const int32_t* part2Node_ptr,
+                       const int32_t* part2Node_col, int num_uniqparts, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  int rc = check_common(plan, where, num_nodes, row_begin, row_end);
+  if (rc) return rc;
+  if (num_uniqparts < 0) { set_error("num_uniqparts < 0"); return ROF_ERR_BAD_ARGUMENT; }
+  HostArray col, up, np_, nc;
+  const int64_t nptr = num_uniqparts ? (int64_t)num_uniqparts + 1 : 0;
+  if ((rc = col.fetch(uniqpart_column_index, num_column_index, where, stream, "uniqpart_column_index"))) return rc;
+  if ((rc = up.fetch(uniqpart_pointers, nptr, where, stream, "uniqpart_pointers"))) return rc;
+  if ((rc = np_.fetch(part2Node_ptr, nptr, where, stream, "part2Node_ptr"))) return rc;
+  if ((rc = sync_if_device(where, stream))) return rc;
+  const int64_t n_nc = num_uniqparts ? np_.ptr[num_uniqparts] : 0;
+  if (n_nc < 0) return bad_layout("part2Node_ptr ends below zero");
+  if ((rc = nc.fetch(part2Node_col, n_nc, where, stream, "part2Node_col"))) return rc;
+  if ((rc = sync_if_device(where, stream))) return rc;
+  if ((rc = check_pointers(up.ptr, num_uniqparts, num_column_index, "uniqpart_pointers"))) return rc;
+  if ((rc = check_pointers(np_.ptr, num_uniqparts, n_nc, "part2Node_ptr"))) return rc;
+  if ((rc = check_ids(col.ptr, num_column_index, num_nodes, "uniqpart_column_index"))) return rc;
+  if ((rc = check_ids(nc.ptr, n_nc, num_nodes, "part2Node_col"))) return rc;
+
+  HostPlan hp;
+  hp.num_nodes = num_nodes; hp.row_begin = row_begin; hp.row_end = row_end;
+  const int rows = row_end - row_begin;
+  try {
+    // A unique part becomes a reuse group when at least two destinations of this plan's
+    // row block share it and it has at least two sources; otherwise its sources are
+    // listed inline in the destination's row (a one-source "partial" is the source itself).
+    std::vector<int32_t> group_of((size_t)num_uniqparts, -1);
+    hp.group_ptr.assign(1, 0);
+    hp.row_ptr.assign((size_t)rows + 1, 0);
+    for (int u = 0; u < num_uniqparts; ++u) {
+      const int32_t len = up.ptr[u + 1] - up.ptr[u];
+      int local = 0;
+      for (int32_t k = np_.ptr[u]; k < np_.ptr[u + 1]; ++k) local += (nc.ptr[k] >= row_begin && nc.ptr[k] < row_end);
+      if (local == 0 || len == 0) continue;
+      const bool grouped = local >= 2 && len >= 2;
+      if (grouped) {
+        group_of[u] = (int32_t)hp.group_ptr.size() - 1;
+        hp.group_col.insert(hp.group_col.end(), col.ptr + up.ptr[u], col.ptr + up.ptr[u + 1]);
+        hp.group_ptr.push_back((int32_t)hp.group_col.size());
+      }
+      for (int32_t k = np_.ptr[u]; k < np_.ptr[u + 1]; ++k) {
+        int v = nc.ptr[k];
+        if (v < row_begin || v >= row_end) continue;
+        hp.row_ptr[(size_t)(v - row_begin) + 1] += grouped ? 1 : len;
+        hp.original_edges += len;
+      }
+    }
+    for (int r = 0; r < rows; ++r) hp.row_ptr[r + 1] += hp.row_ptr[r];
+    hp.col.resize((size_t)hp.row_ptr[rows]);
+    std::vector<int64_t> pos(hp.row_ptr.begin(), hp.row_ptr.end() - 1);
+    for (int u = 0; u < num_uniqparts; ++u) {
+      const int32_t len = up.ptr[u + 1] - up.ptr[u];
+      if (len == 0) continue;
+      for (int32_t k = np_.ptr[u]; k < np_.ptr[u + 1]; ++k) {
+        int v = nc.ptr[k];
+        if (v < row_begin || v >= row_end) continue;
+        int64_t& w = pos[(size_t)(v - row_begin)];
+        if (group_of[u] >= 0) {
+          hp.col[(size_t)w++] = num_nodes + group_of[u];
+        } else {
+          for (int32_t s = up.ptr[u]; s < up.ptr[u + 1]; ++s) hp.col[(size_t)w++] = col.ptr[s];
+        }
+      }
+    }
+  } catch (const std::bad_alloc&) {
+    set_error("out of host memory while building the plan");
+    return ROF_ERR_NO_MEMORY;
+  }
+  return finalize_plan(hp, plan, stream);
+}
+
+int rof_plan_export(const rof_plan* p, int64_t* row_ptr, int32_t* col, int32_t* group_ptr, int32_t* group_col,
+                    int32_t* items, int32_t* split_rows) {
+  if (p == nullptr) { set_error("rof_plan_export: null plan"); return ROF_ERR_BAD_ARGUMENT; }
+  if (row_ptr) std::memcpy(row_ptr, p->h_row_ptr.data(), sizeof(int64_t) * p->h_row_ptr.size());
+  if (group_ptr) std::memcpy(group_ptr, p->h_group_ptr.data(), sizeof(int32_t) * p->h_group_ptr.size());
+  if (items) std::memcpy(items, p->h_items.data(), sizeof(WorkItem) * p->h_items.size());
+  if (split_rows) std::memcpy(split_rows, p->h_split.data(), sizeof(SplitRow) * p->h_split.size());
+  const size_t nb = sizeof(int32_t) * (size_t)p->gather_entries, ng = sizeof(int32_t) * (size_t)p->group_sources;
+  if (p->device < 0) {
+    if (col && nb) std::memcpy(col, p->h_col.data(), nb);
+    if (group_col && ng) std::memcpy(group_col, p->h_col.data() + p->gather_entries, ng);
+    return ROF_OK;
+  }
+  cudaError_t e = cudaSuccess;
+  if (col && nb) e = cudaMemcpy(col, p->d_col, nb, cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess && group_col && ng) e = cudaMemcpy(group_col, p->d_col + p->gather_entries, ng, cudaMemcpyDeviceToHost);
+  return e == cudaSuccess ? ROF_OK : cuda_fail(e, "rof_plan_export");
+}
+
+void rof_plan_destroy(rof_plan* p) {
+  if (p == nullptr) return;
+  cudaFree(p->d_col);
+  cudaFree(p->d_items);
+  cudaFree(p->d_group_items);
+  cudaFree(p->d_split);
+  delete p;
+}
+
+int rof_plan_get_info(const rof_plan* p, rof_plan_info* info) {
+  if (p == nullptr || info == nullptr) { set_error("rof_plan_get_info: null argument"); return ROF_ERR_BAD_ARGUMENT; }
+  info->num_nodes = p->num_nodes;
+  info->row_begin = p->row_begin;
+  info->row_end = p->row_end;
+  info->num_groups = p->num_groups;
+  info->group_sources = p->group_sources;
+  info->gather_entries = p->gather_entries;
+  info->partial_entries = p->partial_entries;
+  info->original_edges = p->original_edges;
+  info->num_items = p->num_items;
+  info->split_rows = p->num_split_rows;
+  info->num_slots = p->num_slots;
+  info->segment_edges = kSegmentEdges;
+  return ROF_OK;
+}
+
+}  // extern "C"

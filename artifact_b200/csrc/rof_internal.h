@@ -1,0 +1,116 @@
+// Internal declarations shared by plan.cu, kernels.cu and api.cu.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+#include <vector>
+
+#include "rof_b200.h"
+
+namespace rof {
+
+// One unit of gather work: sum the rows named by col[begin, end) and store the result.
+//   dst >= 0 : final output row (global id; the kernel subtracts row_begin), scaled per mode
+//   dst <  0 : segment of a split row; the unscaled sum goes to scratch slot (-dst - 1)
+struct __align__(16) WorkItem {
+  int32_t begin;
+  int32_t end;
+  int32_t dst;
+  int32_t pad;
+};
+
+// Second-stage reduce of a split row: out[row] = scale * (slot[first] + ... + slot[first+count-1]).
+struct __align__(16) SplitRow {
+  int32_t row;
+  int32_t first_slot;
+  int32_t count;
+  int32_t pad;
+};
+
+constexpr int kSegmentEdges = 1024;  // longest run of entries one work item sums
+
+}  // namespace rof
+
+struct rof_plan {
+  int device = 0;         // -1: built on a machine without a CUDA device (inspection only)
+  int num_nodes = 0;
+  int row_begin = 0, row_end = 0;
+  int num_groups = 0;
+  int64_t group_sources = 0;
+  int64_t gather_entries = 0;
+  int64_t partial_entries = 0;
+  int64_t original_edges = 0;
+  int num_items = 0;      // phase B
+  int num_split_rows = 0;
+  int num_slots = 0;
+
+  // device arrays
+  int32_t* d_col = nullptr;           // [gather_entries + group_sources]: phase-B entries, then group sources
+  rof::WorkItem* d_items = nullptr;   // [num_items] phase B, longest first
+  rof::WorkItem* d_group_items = nullptr;  // [num_groups] phase A (begin/end index d_col)
+  rof::SplitRow* d_split = nullptr;   // [num_split_rows]
+
+  // host copies kept for rof_plan_export*(): the small arrays always, the entry arrays
+  // only when there is no device to read them back from
+  std::vector<int64_t> h_row_ptr;
+  std::vector<int32_t> h_group_ptr;
+  std::vector<rof::WorkItem> h_items;
+  std::vector<rof::SplitRow> h_split;
+  std::vector<int32_t> h_col;
+};
+
+namespace rof {
+
+void set_error(const std::string& msg);
+const std::string& last_error();
+int cuda_fail(cudaError_t e, const char* what);
+
+// Host-side description of a plan before upload (produced by the three layout readers).
+struct HostPlan {
+  int num_nodes = 0, row_begin = 0, row_end = 0;
+  // destination-major entries of the rows in [row_begin,row_end): row r owns
+  // entries [row_ptr[r-row_begin], row_ptr[r-row_begin+1])
+  std::vector<int64_t> row_ptr;
+  std::vector<int32_t> col;           // < num_nodes: feature row; >= num_nodes: partial row (col - num_nodes)
+  std::vector<int32_t> group_ptr;     // [G+1] into group_col
+  std::vector<int32_t> group_col;     // sources of each group
+  int64_t original_edges = 0;
+};
+
+int finalize_plan(const HostPlan& hp, rof_plan** out, cudaStream_t stream);
+
+struct GatherArgs {
+  const WorkItem* items;
+  int num_items;
+  const int32_t* col;
+  const float* x;        int64_t ldx;        // feature rows (col < num_nodes)
+  const float* partials; int64_t ldp;        // partial rows (col >= num_nodes); may be null in phase A
+  const float* degrees;
+  float* out;            int64_t ldo;        // dst >= 0
+  float* slots;          int64_t lds;        // dst < 0
+  float* mirror;         int64_t ldm;        // optional second copy of the dst>=0 rows
+  int mirror_flag_col;                       // column of `mirror` that receives 1.0f per row, or -1
+  int num_nodes;
+  int row_begin;
+  int dim;
+  int weight_gcn;   // multiply each feature row by rsqrt(degrees[col])
+  int scale_mode;   // 0 none, 1 rsqrt(degrees[dst]), 2 1/degrees[dst]
+};
+
+struct ReduceArgs {
+  const SplitRow* rows;
+  int num_rows;
+  const float* slots; int64_t lds;
+  const float* degrees;
+  float* out;         int64_t ldo;
+  int row_begin;
+  int dim;
+  int scale_mode;
+};
+
+// Launchers (kernels.cu).  Return cudaSuccess or the launch error.
+cudaError_t launch_gather(const GatherArgs& a, cudaStream_t stream);
+cudaError_t launch_split_reduce(const ReduceArgs& a, cudaStream_t stream);
+
+}  // namespace rof

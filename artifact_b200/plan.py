@@ -1,0 +1,215 @@
+"""AggregationPlan: Python handle of a `rof_plan` (include/rof_b200.h).
+
+A plan is built once per graph from upstream's index tensors (the fields of `ROF_inputInfo`,
+ROF_evaluation/ROF_main.py:164-174) and then drives every aggregation pass.  torch is used
+only to allocate device memory and to name the current stream.
+"""
+import ctypes
+
+import numpy as np
+import torch
+
+from . import _native
+
+MODES = {"gcn": 0, "sum": 1, "mean": 2}
+ON_HOST, ON_DEVICE = 0, 1
+
+
+def _as_index(a):
+    """-> (keepalive, pointer, length, where) for a torch tensor or numpy array of int32."""
+    if isinstance(a, torch.Tensor):
+        if a.dtype != torch.int32:
+            raise TypeError(f"index tensors must be int32 (upstream casts them at ROF_main.py:143-161), got {a.dtype}")
+        if not a.is_contiguous():
+            raise RuntimeError("index tensor must be contiguous")
+        return a, ctypes.c_void_p(a.data_ptr()), a.numel(), (ON_DEVICE if a.is_cuda else ON_HOST)
+    a = np.ascontiguousarray(a)
+    if a.dtype != np.int32:
+        if a.dtype in (np.uint32, np.int64) and (a.size == 0 or (a.min() >= 0 and a.max() < 2 ** 31)):
+            a = a.astype(np.int32)
+        else:
+            raise TypeError(f"index arrays must be int32, got {a.dtype}")
+    return a, ctypes.c_void_p(a.ctypes.data), a.size, ON_HOST
+
+
+def _same_place(parts):
+    wh = {w for (_, _, _, w) in parts}
+    if len(wh) != 1:
+        raise RuntimeError("all index tensors of one layout must live in the same place (all host or all device)")
+    return wh.pop()
+
+
+class AggregationPlan:
+    def __init__(self, handle, layout, device, keep):
+        self._h = handle
+        self.layout = layout
+        self.device = device
+        self._keep = keep          # index tensors this plan was built from (pins their addresses)
+        self._workspace = None
+        info = _native.PlanInfo()
+        _native.check(_native.cuda().rof_plan_get_info(self._h, ctypes.byref(info)))
+        self.info = {n: int(getattr(info, n)) for n, _ in _native.PlanInfo._fields_}
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            try:
+                _native.cuda().rof_plan_destroy(h)
+            except Exception:
+                pass
+
+    # -- constructors ------------------------------------------------------------------
+    @staticmethod
+    def _stream(device):
+        if device is not None and torch.cuda.is_available():
+            return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        return ctypes.c_void_p(0)
+
+    @staticmethod
+    def _device_of(keep):
+        for t in keep:
+            if isinstance(t, torch.Tensor) and t.is_cuda:
+                return t.device
+        return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else None
+
+    @classmethod
+    def from_parts(cls, num_nodes, column_index, part_pointers, part2Node, rows=None, device=None):
+        """Original part layout (upstream `SAG` / `GNNA_*`, reuse_conv.cpp:132-205)."""
+        ci, pp, pn = map(_as_index, (column_index, part_pointers, part2Node))
+        where = _same_place([ci, pp, pn])
+        keep = [ci[0], pp[0], pn[0]]
+        device = device or cls._device_of(keep)
+        r0, r1 = rows if rows is not None else (0, num_nodes)
+        h = ctypes.c_void_p()
+        with _device_guard(device):
+            _native.check(_native.cuda().rof_plan_create_parts(
+                ctypes.byref(h), where, num_nodes, r0, r1, ci[1], ci[2], pp[1], pn[1], pn[2], cls._stream(device)))
+        return cls(h, "parts", device, keep)
+
+    @classmethod
+    def from_v1(cls, num_nodes, column_index, part_pointers, part2Node, part_cache_flagindex,
+                part_pointers_cache, column_index_cache, rows=None, device=None):
+        """ROF_v1 layout (upstream `reuse_*_v1`, reuse_conv.cpp:208-285)."""
+        ci, pp, pn, fl, pc, cc = map(_as_index, (column_index, part_pointers, part2Node, part_cache_flagindex,
+                                                  part_pointers_cache, column_index_cache))
+        where = _same_place([ci, pp, pn, fl, pc, cc])
+        keep = [ci[0], pp[0], pn[0], fl[0], pc[0], cc[0]]
+        device = device or cls._device_of(keep)
+        r0, r1 = rows if rows is not None else (0, num_nodes)
+        groups = max(0, pc[2] - 1)
+        h = ctypes.c_void_p()
+        with _device_guard(device):
+            _native.check(_native.cuda().rof_plan_create_v1(
+                ctypes.byref(h), where, num_nodes, r0, r1, ci[1], ci[2], pp[1], pn[1], pn[2], fl[1], pc[1], cc[1],
+                groups, cls._stream(device)))
+        return cls(h, "v1", device, keep)
+
+    @classmethod
+    def from_v2(cls, num_nodes, uniqpart_column_index, uniqpart_pointers, part2Node_ptr, part2Node_col,
+                rows=None, device=None):
+        """ROF_v2 layout (upstream `reuse_*_v2`, reuse_conv.cpp:288-346)."""
+        ci, up, np_, nc = map(_as_index, (uniqpart_column_index, uniqpart_pointers, part2Node_ptr, part2Node_col))
+        where = _same_place([ci, up, np_, nc])
+        keep = [ci[0], up[0], np_[0], nc[0]]
+        device = device or cls._device_of(keep)
+        r0, r1 = rows if rows is not None else (0, num_nodes)
+        h = ctypes.c_void_p()
+        with _device_guard(device):
+            _native.check(_native.cuda().rof_plan_create_v2(
+                ctypes.byref(h), where, num_nodes, r0, r1, ci[1], ci[2], up[1], np_[1], nc[1], max(0, up[2] - 1),
+                cls._stream(device)))
+        return cls(h, "v2", device, keep)
+
+    # -- inspection --------------------------------------------------------------------
+    def export(self):
+        i = self.info
+        rows = i["row_end"] - i["row_begin"]
+        out = {
+            "row_ptr": np.zeros(rows + 1, np.int64), "col": np.zeros(i["gather_entries"], np.int32),
+            "group_ptr": np.zeros(i["num_groups"] + 1, np.int32), "group_col": np.zeros(i["group_sources"], np.int32),
+            "items": np.zeros((i["num_items"], 4), np.int32), "split_rows": np.zeros((i["split_rows"], 4), np.int32),
+        }
+        p = lambda a: ctypes.c_void_p(a.ctypes.data)
+        _native.check(_native.cuda().rof_plan_export(self._h, p(out["row_ptr"]), p(out["col"]), p(out["group_ptr"]),
+                                                     p(out["group_col"]), p(out["items"]), p(out["split_rows"])))
+        return out
+
+    def workspace_bytes(self, dim):
+        return int(_native.cuda().rof_plan_workspace_bytes(self._h, int(dim)))
+
+    def algorithmic_bytes(self, dim, mode="gcn"):
+        return int(_native.cuda().rof_plan_algorithmic_bytes(self._h, int(dim), MODES[mode]))
+
+    # -- the hot call ------------------------------------------------------------------
+    def _get_workspace(self, nbytes, device):
+        ws = self._workspace
+        if ws is None or ws.numel() < nbytes or ws.device != device:
+            # torch's caching allocator returns 512-byte aligned blocks
+            ws = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=device)
+            self._workspace = ws
+        return ws
+
+    def aggregate(self, x, degrees=None, mode="gcn", out=None, cache_result=None, workspace=None, phases=7):
+        """out[v] = scale(v) * sum over v's gathered rows; see rof_aggregate() in include/rof_b200.h.
+        `x` is [num_nodes, dim] fp32 on the GPU; returns a new [rows, dim] tensor unless `out` is given."""
+        if not x.is_cuda:
+            raise RuntimeError("x must be a CUDA tensor")            # upstream CHECK_CUDA, reuse_conv.cpp:121
+        if x.dtype != torch.float32 or x.dim() != 2:
+            raise RuntimeError("x must be a 2-D float32 tensor")
+        if x.stride(1) != 1 and x.size(1) > 1:
+            raise RuntimeError("x must be contiguous")               # upstream CHECK_CONTIGUOUS, reuse_conv.cpp:122
+        i = self.info
+        if x.size(0) != i["num_nodes"]:
+            raise RuntimeError(f"x has {x.size(0)} rows, the plan was built for {i['num_nodes']} nodes")
+        dim = x.size(1)
+        rows = i["row_end"] - i["row_begin"]
+        if out is None:
+            out = torch.empty((rows, dim), dtype=torch.float32, device=x.device)
+        elif (out.dtype != torch.float32 or not out.is_cuda or out.dim() != 2 or out.size(0) != rows
+              or out.size(1) != dim or (out.stride(1) != 1 and dim > 1)):
+            raise RuntimeError("out must be a float32 CUDA tensor of shape [rows, dim] with unit column stride")
+        m = MODES[mode]
+        deg_ptr = None
+        if m != MODES["sum"]:
+            if degrees is None or not degrees.is_cuda or degrees.dtype != torch.float32 or not degrees.is_contiguous():
+                raise RuntimeError("degrees must be a contiguous float32 CUDA tensor")
+            if degrees.numel() != i["num_nodes"]:
+                raise RuntimeError("degrees must have one entry per node")
+            deg_ptr = ctypes.c_void_p(degrees.data_ptr())
+        cache_ptr = None
+        if cache_result is not None:
+            if (not cache_result.is_cuda or cache_result.dtype != torch.float32 or not cache_result.is_contiguous()
+                    or tuple(cache_result.shape) != (i["num_groups"], dim + 1)):
+                raise RuntimeError(f"part_result_cache must be a contiguous float32 CUDA tensor of shape "
+                                   f"[{i['num_groups']}, {dim + 1}]")
+            cache_ptr = ctypes.c_void_p(cache_result.data_ptr())
+        need = self.workspace_bytes(dim)
+        ws = workspace if workspace is not None else (self._get_workspace(need, x.device) if need else None)
+        ldx = x.stride(0) if x.size(0) > 1 else dim
+        ldo = out.stride(0) if rows > 1 else dim
+        with _device_guard(x.device):
+            stream = ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
+            _native.check(_native.cuda().rof_aggregate_phases(
+                self._h, int(phases), m, ctypes.c_void_p(x.data_ptr()), ldx, dim, deg_ptr, ctypes.c_void_p(out.data_ptr()), ldo,
+                cache_ptr, ctypes.c_void_p(ws.data_ptr()) if ws is not None else None,
+                ws.numel() if ws is not None else 0, stream))
+        return out
+
+    @staticmethod
+    def last_launch_count():
+        return int(_native.cuda().rof_last_launch_count())
+
+
+class _device_guard:
+    def __init__(self, device):
+        self.device = device
+        self.ctx = None
+
+    def __enter__(self):
+        if self.device is not None and torch.cuda.is_available():
+            self.ctx = torch.cuda.device(self.device)
+            self.ctx.__enter__()
+
+    def __exit__(self, *a):
+        if self.ctx is not None:
+            self.ctx.__exit__(*a)

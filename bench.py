@@ -1,0 +1,466 @@
+#!/usr/bin/env python
+"""Benchmark of the reuse aggregation hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c4|c5] [--dim D]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference ...      # CPU plain aggregation on the host cores
+
+One *step* is one forward plus one backward aggregation pass (the backward applies the same
+operator to the incoming gradient, reuse_conv.py:76-92) of fp32 features of width D over the
+seeded synthetic graph of the workload, through the reuse plan built from the ROF_v2 layout.
+`value` is edges/s with the ORIGINAL edge count (reuse shows up as more edges per second),
+inputs resident in HBM; `e2e` is the same step through the public API with pinned-host inputs
+and outputs, copies inside the timed region.  With N > 1 the destination rows are cut into N
+equal blocks, every pass first all-gathers the feature blocks over NCCL, and the same total
+work is divided (strong scaling).  Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (config function key, default feature width, part_size, mode)
+    "c2": ("c2", 256, 2, "sum"),
+    "c4": ("c4", 256, 2, "gcn"),
+    "c5": ("c5", 64, 2, "sum"),
+}
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.gpu), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        inside = [l for (t, l) in self.lines if t0 - 0.2 <= t <= t1 + 0.3] or [l for (_, l) in self.lines]
+        for l in inside:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def build_graph(name, scale):
+    from artifact_b200 import graphs
+    return graphs.CONFIGS[WORKLOADS[name][0]](scale)
+
+
+# --------------------------------------------------------------------------------------------
+# reference arm: the reuse-free CSR gather-sum on the host cores (C/OpenMP restatement; upstream
+# has no CPU implementation of this path, reuse_conv.cpp:238,278,310,341)
+# --------------------------------------------------------------------------------------------
+def cpu_plain(g, dim, mode, seconds_budget, steps=1, warmup=0, threads=0):
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import rof_oracle
+    n = g.num_nodes
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal((n, dim), dtype=np.float32)
+    deg = np.maximum(g.degrees_f32(), 1.0)
+    out = np.zeros((n, dim), np.float32)
+    cores = threads or rof_oracle.max_threads()
+    ip = g.indptr_dst
+    # probe ~1% of the edges to size a sample that fits the budget
+    r_probe = int(np.searchsorted(ip, max(1, g.num_edges // 100)))
+    t = time.perf_counter()
+    rof_oracle.plain_csr(x, ip, g.indices_src, deg, mode, rows=(0, max(1, r_probe)), num_threads=cores, out=out)
+    rate = max(ip[max(1, r_probe)], 1) / max(time.perf_counter() - t, 1e-6)            # edges/s, cold
+    per_step = seconds_budget / max(steps + warmup, 1)
+    want_edges = int(min(g.num_edges, max(rate * per_step, g.num_edges * 0.01)))
+    r1 = int(np.searchsorted(ip, want_edges))
+    r1 = min(max(r1, 1), n)
+    edges = int(ip[r1])
+    times = []
+    for i in range(warmup + steps):
+        t = time.perf_counter()
+        for _ in range(2):                                 # forward + backward pass, like the GPU step
+            rof_oracle.plain_csr(x, ip, g.indices_src, deg, mode, rows=(0, r1), num_threads=cores, out=out)
+        dt = time.perf_counter() - t
+        if i >= warmup:
+            times.append(dt)
+    ms = 1e3 * float(np.mean(times))
+    return {"value": 2 * edges / (ms / 1e3), "unit": "edges/s", "cores": int(cores), "kind": "port",
+            "sample": f"rows [0,{r1}) of the workload = {edges} of {g.num_edges} edges, fwd+bwd, D={dim}, "
+                      f"{steps} step(s)", "ms_per_step": ms}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl, dim, ps, mode = args.workload, args.dim, args.part_size, args.mode
+    g = build_graph(wl, args.scale)
+    cb = cpu_plain(g, dim, mode, seconds_budget=120.0, steps=args.steps, warmup=args.warmup)
+    line = {
+        "impl": "reference", "metric": "aggregation edges/s", "value": cb["value"], "unit": "edges/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_step"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, g, None),
+        "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cb["value"], "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+_V2_KEYS = ("uniqpart_column_index", "uniqpart_pointers", "part2Node_ptr", "part2Node_col", "picked_fanout",
+            "part2Node")
+
+
+def prepare_workload(args, rank, world):
+    """-> (graph, layouts needed for the ROF_v2 plan, seconds for graph, seconds for search)"""
+    from artifact_b200 import graphs, search
+    cache_dir = os.environ.get("ROF_CACHE_DIR", "/tmp/rof_b200_cache")
+    path = os.path.join(cache_dir, f"{args.workload}_scale{args.scale}_ps{args.part_size}.npz")
+    t_graph = t_search = 0.0
+
+    def compute():
+        t0 = time.time()
+        g = build_graph(args.workload, args.scale)
+        tg = time.time() - t0
+        t0 = time.time()
+        L = search.search_graph(g, args.part_size)
+        return g, L, tg, time.time() - t0
+
+    def load():
+        z = np.load(path)
+        g = graphs.Graph(args.workload, int(z["num_nodes"]), z["indptr_dst"], z["indices_src"], None, None,
+                         bool(z["symmetric"]), 0)
+        L = {k: z[k] for k in _V2_KEYS}
+        L["part_size"] = args.part_size
+        L["original_column_index"] = g.indices_src
+        return g, L
+
+    if os.path.exists(path):
+        try:
+            t0 = time.time()
+            g, L = load()
+            return g, L, time.time() - t0, 0.0
+        except Exception:
+            pass
+    result = None
+    if rank == 0:
+        g, L, t_graph, t_search = result = compute()
+        try:
+            os.makedirs(cache_dir, exist_ok=True)
+            tmp = path + f".tmp{os.getpid()}.npz"
+            np.savez(tmp, num_nodes=np.int64(g.num_nodes), symmetric=np.int64(g.symmetric), indptr_dst=g.indptr_dst,
+                     indices_src=g.indices_src, **{k: L[k] for k in _V2_KEYS})
+            os.replace(tmp, path)
+        except Exception:
+            pass
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    if result is None:
+        try:
+            g, L = load()
+        except Exception:
+            g, L, t_graph, t_search = compute()
+        return g, L, t_graph, t_search
+    return result
+
+
+def workload_config(args, g, ratios):
+    c = {"workload": f"{args.workload}: seeded synthetic graph N={g.num_nodes} E={g.num_edges}, fp32 features "
+                     f"D={args.dim}, {args.mode} aggregation, forward+backward pass per step",
+         "part_size": args.part_size, "layout": "ROF_v2", "scale": args.scale,
+         "l2": "feature matrix and index arrays together exceed L2 (126 MB); no flush between iterations",
+         "parallelism": f"row-block x{args.gpus}" if args.gpus > 1 else "single GPU"}
+    if ratios is not None:
+        c["reuse"] = ratios
+    return c
+
+
+# --------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--dim", type=int, default=0)
+    ap.add_argument("--part-size", type=int, default=0)
+    ap.add_argument("--mode", default="")
+    ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (tests / profiling only)")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--only-kernel", action="store_true", help="skip sweep, CPU baseline and e2e (profiling)")
+    args = ap.parse_args()
+    _, d_dim, d_ps, d_mode = WORKLOADS[args.workload]
+    args.dim = args.dim or d_dim
+    args.part_size = args.part_size or d_ps
+    args.mode = args.mode or d_mode
+    args.warmup = max(args.warmup, 3)
+    if args.only_kernel:
+        args.no_sweep = args.no_cpu = True
+
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    from artifact_b200 import search
+    from artifact_b200.plan import AggregationPlan
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the aggregation path has no CPU fallback")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    hbm_peak, peak_kind = load_peaks()
+
+    # ---- workload: graph -> reuse search -> plans ------------------------------------------
+    # Everything is seeded, so every rank could compute it; to keep the host cores for one
+    # search, rank 0 computes and leaves the arrays in a cache directory the other ranks (and
+    # the next invocation on the same box) load.
+    g, L, t_graph, t_search = prepare_workload(args, rank, world)
+    n, E, D, mode = g.num_nodes, g.num_edges, args.dim, args.mode
+    ratios = search.reuse_ratios(L)
+    blk = (n + world - 1) // world
+    n_pad = blk * world
+    r0, r1 = min(rank * blk, n), min((rank + 1) * blk, n)
+    t0 = time.time()
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32))
+    v2 = [i32(L[k]) for k in ("uniqpart_column_index", "uniqpart_pointers", "part2Node_ptr", "part2Node_col")]
+    plan = AggregationPlan.from_v2(n, *v2, rows=(r0, r1), device=dev)
+    plain = AggregationPlan.from_parts(n, i32(g.indices_src), i32(g.indptr_dst), i32(np.arange(n)), rows=(r0, r1),
+                                       device=dev)
+    t_plan = time.time() - t0
+    del v2
+    my_edges = int(g.indptr_dst[r1] - g.indptr_dst[r0])
+    deg = torch.from_numpy(np.maximum(g.degrees_f32(), 1.0)).to(dev)
+
+    gen = torch.Generator(device=dev); gen.manual_seed(1234)
+    x_full = torch.empty((n_pad, D), device=dev)
+    g_full = torch.empty((n_pad, D), device=dev)
+    x_full.normal_(generator=gen); g_full.normal_(generator=gen)
+    x_loc = x_full[rank * blk:(rank + 1) * blk].clone()
+    g_loc = g_full[rank * blk:(rank + 1) * blk].clone()
+    out_f = torch.empty((r1 - r0, D), device=dev)
+    out_b = torch.empty((r1 - r0, D), device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    gather_events = []
+    launches = [0]
+
+    def one_pass(p, src_loc, src_full, out, timed_gather=False):
+        if world > 1:
+            dist.all_gather_into_tensor(src_full, src_loc)
+        xs = src_full[:n]
+        if timed_gather:
+            p.aggregate(xs, deg, mode, out=out, phases=1); launches[0] += p.last_launch_count()
+            e0, e1 = ev(), ev()
+            e0.record()
+            p.aggregate(xs, deg, mode, out=out, phases=2); launches[0] += p.last_launch_count()
+            e1.record()
+            p.aggregate(xs, deg, mode, out=out, phases=4); launches[0] += p.last_launch_count()
+            gather_events.append((e0, e1))
+        else:
+            p.aggregate(xs, deg, mode, out=out); launches[0] += p.last_launch_count()
+
+    def step(p, timed_gather=False):
+        one_pass(p, x_loc, x_full, out_f, timed_gather)
+        one_pass(p, g_loc, g_full, out_b, timed_gather)
+
+    def timed(p, steps, warmup, timed_gather=False):
+        for _ in range(warmup):
+            step(p)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        launches[0] = 0
+        s, e = ev(), ev()
+        w0 = time.time()
+        s.record()
+        for _ in range(steps):
+            step(p, timed_gather)
+        e.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        w1 = time.time()
+        ms = torch.tensor([s.elapsed_time(e)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()) / steps, w0, w1
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.3)
+    ms_step, w0, w1 = timed(plan, args.steps, args.warmup, timed_gather=True)
+    clocks = sampler.stop(w0, w1) if sampler else None
+    n_launch = launches[0]
+    value = 2.0 * E / (ms_step / 1e3)
+
+    # dominant kernel: the phase-B gather of this rank's block, timed by events inside the steps
+    gms = float(np.mean([a.elapsed_time(b) for a, b in gather_events]))
+    info = plan.info
+    row_b = 4.0 * D
+    gather_bytes = row_b * (info["gather_entries"] + (r1 - r0)) + 4.0 * info["gather_entries"] + 4.0 * (r1 - r0 + 1)
+    if mode == "gcn":
+        gather_bytes += 4.0 * (info["gather_entries"] - info["partial_entries"])
+    achieved = gather_bytes / (gms / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                "traffic": None, "kernel": "gather_rows_kernel (phase B)", "ms_per_launch": gms,
+                "algorithmic_bytes_per_launch": gather_bytes, "peak_kind": f"{peak_kind} copy bandwidth",
+                "note": "algorithmic bytes = (gathered rows + written rows) x 4D + 4 per index; hub rows are "
+                        "re-read from L2, so achieved can exceed the DRAM peak; see profiles/ for DRAM traffic"}
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        try:
+            t = json.load(open(traffic_file)).get(f"{args.workload}:D{D}:{mode}")
+            if t and world == 1 and args.scale == 1.0:
+                roofline["traffic"] = t["dram_bytes_per_launch"]
+        except Exception:
+            pass
+
+    extra = {}
+    if world == 1:
+        ms_plain, _, _ = timed(plain, max(3, args.steps // 2), 3)
+        extra["plain"] = {"ms_per_step": ms_plain, "edges_per_s": 2.0 * E / (ms_plain / 1e3),
+                          "algorithmic_GBs": 2 * plain.algorithmic_bytes(D, mode) / ms_plain / 1e6}
+        extra["reuse"] = {"ms_per_step": ms_step, "edges_per_s": value,
+                          "algorithmic_GBs": 2 * plan.algorithmic_bytes(D, mode) / ms_step / 1e6}
+
+    # ---- end to end through the public API with host buffers -----------------------------------
+    h_x = torch.empty((blk, D), pin_memory=True); h_x.copy_(x_loc)
+    h_g = torch.empty((blk, D), pin_memory=True); h_g.copy_(g_loc)
+    h_of = torch.empty((r1 - r0, D), pin_memory=True)
+    h_ob = torch.empty((r1 - r0, D), pin_memory=True)
+
+    def e2e_step():
+        x_loc.copy_(h_x, non_blocking=True)
+        one_pass(plan, x_loc, x_full, out_f)
+        h_of.copy_(out_f, non_blocking=True)
+        g_loc.copy_(h_g, non_blocking=True)
+        one_pass(plan, g_loc, g_full, out_b)
+        h_ob.copy_(out_b, non_blocking=True)
+
+    e2e_steps = max(3, min(args.steps, 10))
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    s, e = ev(), ev()
+    s.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e.record()
+    torch.cuda.synchronize()
+    ms_e2e = torch.tensor([s.elapsed_time(e) / e2e_steps], device=dev)
+    if world > 1:
+        dist.all_reduce(ms_e2e, op=dist.ReduceOp.MAX)
+    ms_e2e = float(ms_e2e.item())
+    e2e = {"value": 2.0 * E / (ms_e2e / 1e3), "unit": "edges/s", "ms_per_step": ms_e2e,
+           "h2d_bytes_per_step": 2 * blk * D * 4 * world, "d2h_bytes_per_step": 2 * n * D * 4,
+           "note": "features and gradients copied from pinned host memory, both results copied back, every step; "
+                   "the graph plan stays resident like upstream's inputInfo tensors"}
+
+    # ---- width / mode sweep (single GPU only; informational) -----------------------------------
+    if world == 1 and not args.no_sweep:
+        sweep = []
+        for d in (32, 64, 128, 256, 602):
+            xs = torch.randn((n, d), device=dev)
+            o = torch.empty((n, d), device=dev)
+            for m in ("sum", "mean"):
+                row = {"D": d, "mode": m}
+                for nm, p in (("reuse", plan), ("plain", plain)):
+                    for _ in range(3):
+                        p.aggregate(xs, deg, m, out=o)
+                    s, e = ev(), ev()
+                    s.record()
+                    for _ in range(5):
+                        p.aggregate(xs, deg, m, out=o)
+                    e.record(); torch.cuda.synchronize()
+                    ms = s.elapsed_time(e) / 5
+                    row[nm] = {"ms": round(ms, 4), "gedges_per_s": round(E / ms / 1e6, 3),
+                               "algorithmic_GBs": round(p.algorithmic_bytes(d, m) / ms / 1e6, 1)}
+                sweep.append(row)
+            del xs, o
+        extra["sweep_forward_pass"] = sweep
+
+    if rank == 0:
+        cpu = None
+        if world == 1 and not args.no_cpu:
+            cb = cpu_plain(g, D, mode, seconds_budget=20.0)
+            cpu = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        line = {
+            "metric": "aggregation edges/s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args, g, ratios),
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": n_launch, "clocks": clocks,
+            "setup_s": {"graph": round(t_graph, 2), "reuse_search": round(t_search, 2), "plans": round(t_plan, 2)},
+            "shard": {"rows": r1 - r0, "edges_rank0": my_edges},
+        }
+        line.update(extra)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

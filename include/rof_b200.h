@@ -1,0 +1,174 @@
+/*
+ * rof_b200 — C ABI of the B200 (sm_100a) neighbour-aggregation library.
+ *
+ * This is the boundary a host program binds instead of upstream's pybind11 module `ROF`
+ * (ROF/reuse_conv/reuse_conv.cpp:353-365).  Upstream's seven entry points all reduce to
+ * "aggregate a [N, D] fp32 matrix over one of three index layouts"; the dense X.W products
+ * around it (reuse_conv_kernel.cu:302, 382-383, 621, 819-820, 971, 1050-1051) stay with the
+ * caller's BLAS.  Here that is two steps:
+ *
+ *   1. build a plan once per graph from the index tensors exactly as upstream's host-side
+ *      preprocessor emits them (int32; on the host or already on the device);
+ *   2. call rof_aggregate() per layer / per direction with raw device pointers and a stream.
+ *
+ * No function allocates per call except the plan constructors; rof_aggregate() uses only the
+ * caller's workspace.  All functions return a rof_status; none exits the process (upstream
+ * prints and calls exit(-1) on a launch error, reuse_conv_kernel.cu:114-118).  All pointers
+ * are plain C pointers; `stream` is a cudaStream_t passed as void*.
+ */
+#ifndef ROF_B200_H_
+#define ROF_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct rof_plan rof_plan;
+
+enum rof_status {
+  ROF_OK = 0,
+  ROF_ERR_BAD_ARGUMENT = 1,   /* null pointer, negative size, unknown enum value, misaligned ld */
+  ROF_ERR_BAD_LAYOUT = 2,     /* index tensors violate an invariant of the upstream layouts */
+  ROF_ERR_CUDA = 3,           /* a CUDA runtime call failed; see rof_last_error() */
+  ROF_ERR_WORKSPACE = 4,      /* workspace missing, misaligned or smaller than rof_plan_workspace_bytes() */
+  ROF_ERR_NO_MEMORY = 5,      /* host allocation failed while building a plan */
+  ROF_ERR_WAIT_LIMIT = 6      /* a bounded device-side wait gave up (reserved for the multi-GPU pipeline) */
+};
+
+/* What is summed.  Upstream implements GCN (its GNNA / ROF_v1 / ROF_v2 kernels,
+ * reuse_conv_kernel.cu:254,270,276-283) and SUM (its SAG kernel, :185); MEAN is
+ * SUM followed by 1/degrees[dst] (0 for an empty row). */
+enum rof_mode {
+  ROF_MODE_GCN = 0,  /* out[v] = rsqrt(deg[v]) * sum_n rsqrt(deg[n]) * x[n] */
+  ROF_MODE_SUM = 1,  /* out[v] = sum_n x[n] */
+  ROF_MODE_MEAN = 2  /* out[v] = (sum_n x[n]) / deg[v] */
+};
+
+enum rof_location { ROF_ON_HOST = 0, ROF_ON_DEVICE = 1 };
+
+typedef struct rof_plan_info {
+  int64_t num_nodes;        /* N: rows of the feature matrix */
+  int64_t row_begin;        /* first destination row this plan produces */
+  int64_t row_end;          /* one past the last destination row */
+  int64_t num_groups;       /* G: reuse groups whose partial sum is built in phase A */
+  int64_t group_sources;    /* rows gathered by phase A (sum of group sizes) */
+  int64_t gather_entries;   /* rows gathered by phase B: partial rows + residual source rows */
+  int64_t partial_entries;  /* how many of gather_entries are partial rows (sum of fan-outs) */
+  int64_t original_edges;   /* edges the same rows hold without reuse */
+  int64_t num_items;        /* work items of phase B (rows + segments of split rows) */
+  int64_t split_rows;       /* rows cut into segments (second-stage reduce) */
+  int64_t num_slots;        /* segment sums held in scratch between phase B and the reduce */
+  int64_t segment_edges;    /* maximum entries per work item */
+} rof_plan_info;
+
+/*
+ * Plan constructors.  `where` says whether the int32 index arrays are host or device memory
+ * (device arrays are copied to the host once; `stream` orders that copy).  A plan covers the
+ * destination rows [row_begin, row_end) — pass 0 and num_nodes for the whole graph; a
+ * multi-GPU run gives each rank its own block.  Feature rows are always addressed globally.
+ *
+ * rof_plan_create_parts — the original part layout used by upstream's `SAG`, `GNNA_forward`
+ *   and `GNNA_backward` (reuse_conv.cpp:132-205): column_index[num_column_index],
+ *   part_pointers[num_parts+1], part2Node[num_parts].
+ */
+int rof_plan_create_parts(rof_plan** plan, int where, int num_nodes, int row_begin, int row_end,
+                          const int32_t* column_index, int64_t num_column_index,
+                          const int32_t* part_pointers, const int32_t* part2Node, int num_parts,
+                          void* stream);
+
+/*
+ * rof_plan_create_v1 — the ROF_v1 layout of `reuse_forward_v1` / `reuse_backward_v1`
+ *   (reuse_conv.cpp:208-285): the reorganised column_index, part_pointers, part2Node, plus
+ *   part_cache_flagindex[num_parts] (0, or 1 + group id), part_pointers_cache[num_groups+1]
+ *   and column_index_cache[part_pointers_cache[num_groups]].
+ */
+int rof_plan_create_v1(rof_plan** plan, int where, int num_nodes, int row_begin, int row_end,
+                       const int32_t* column_index, int64_t num_column_index,
+                       const int32_t* part_pointers, const int32_t* part2Node, int num_parts,
+                       const int32_t* part_cache_flagindex, const int32_t* part_pointers_cache,
+                       const int32_t* column_index_cache, int num_groups, void* stream);
+
+/*
+ * rof_plan_create_v2 — the ROF_v2 layout of `reuse_forward_v2` / `reuse_backward_v2`
+ *   (reuse_conv.cpp:288-346): uniqpart_column_index, uniqpart_pointers[num_uniqparts+1],
+ *   part2Node_ptr[num_uniqparts+1], part2Node_col[part2Node_ptr[num_uniqparts]].
+ */
+int rof_plan_create_v2(rof_plan** plan, int where, int num_nodes, int row_begin, int row_end,
+                       const int32_t* uniqpart_column_index, int64_t num_column_index,
+                       const int32_t* uniqpart_pointers, const int32_t* part2Node_ptr,
+                       const int32_t* part2Node_col, int num_uniqparts, void* stream);
+
+void rof_plan_destroy(rof_plan* plan);
+int rof_plan_get_info(const rof_plan* plan, rof_plan_info* info);
+
+/*
+ * Copy the plan's derived arrays to host memory for inspection (any pointer may be NULL):
+ *   row_ptr    [row_end-row_begin+1] int64  entry range of each destination row
+ *   col        [gather_entries]      int32  < num_nodes: feature row; >= num_nodes: partial row
+ *   group_ptr  [num_groups+1]        int32  source range of each reuse group
+ *   group_col  [group_sources]       int32
+ *   items      [num_items][4]        int32  (begin, end, dst, 0); dst<0: segment slot -dst-1
+ *   split_rows [split_rows][4]       int32  (row, first_slot, slot_count, 0)
+ * A plan built on a machine without a CUDA device can be exported but not run.
+ */
+int rof_plan_export(const rof_plan* plan, int64_t* row_ptr, int32_t* col, int32_t* group_ptr,
+                    int32_t* group_col, int32_t* items, int32_t* split_rows);
+
+/* Bytes of device scratch rof_aggregate() needs for feature width `dim`: the partial-sum
+ * rows of phase A plus the segment sums of split rows.  256-byte aligned memory. */
+int64_t rof_plan_workspace_bytes(const rof_plan* plan, int dim);
+
+/* Algorithmic bytes of one rof_aggregate() call at width `dim`: 4*dim per gathered row and
+ * per written row (phase A and phase B), plus 4 per index entry read. */
+int64_t rof_plan_algorithmic_bytes(const rof_plan* plan, int dim, int mode);
+
+/*
+ * One aggregation pass: replaces the kernel launches inside upstream's
+ * spmm_forward_cuda_GNNA / reuse_spmm_forward_cuda_v1 / reuse_spmm_forward_cuda_v2 and their
+ * backward twins (reuse_conv_kernel.cu:290-386, 603-823, 957-1054).
+ *
+ *   x        [num_nodes, dim] fp32 device, row stride ldx (elements)
+ *   degrees  [num_nodes] fp32 device (in-degrees as upstream passes them); unused for SUM
+ *   out      [row_end-row_begin, dim] fp32 device, row stride ldo; every row is written
+ *            exactly once (no zero-fill needed, no atomics)
+ *   cache_result  optional [num_groups, dim+1] fp32 device: upstream's `part_result_cache`
+ *            (ROF_v1 only); when given, phase A also stores each partial row and the 1.0
+ *            "ready" flag there like upstream's caching kernel (:479-485).  May be NULL.
+ *   workspace / workspace_bytes  device scratch, see rof_plan_workspace_bytes()
+ *
+ * Work is only enqueued on `stream`; the call does not synchronise.
+ */
+int rof_aggregate(const rof_plan* plan, int mode, const float* x, int64_t ldx, int dim,
+                  const float* degrees, float* out, int64_t ldo, float* cache_result,
+                  void* workspace, int64_t workspace_bytes, void* stream);
+
+/*
+ * The same pass, one phase at a time, for callers that want to time or overlap the phases:
+ * A (ROF_PHASE_PARTIALS) builds the partial-sum rows of the reuse groups into the workspace,
+ * B (ROF_PHASE_GATHER) sums every destination row (reads A's rows), C (ROF_PHASE_REDUCE)
+ * combines the segment sums of split rows.  Phases must be issued in the order A, B, C on one
+ * stream with the same arguments; rof_aggregate() is ROF_PHASE_ALL.  Upstream's counterpart
+ * of A and B are the two launches of ROF_v1 (reuse_conv_kernel.cu:665, 692).
+ */
+enum rof_phase { ROF_PHASE_PARTIALS = 1, ROF_PHASE_GATHER = 2, ROF_PHASE_REDUCE = 4, ROF_PHASE_ALL = 7 };
+
+int rof_aggregate_phases(const rof_plan* plan, int phases, int mode, const float* x, int64_t ldx,
+                         int dim, const float* degrees, float* out, int64_t ldo, float* cache_result,
+                         void* workspace, int64_t workspace_bytes, void* stream);
+
+/* Number of kernel launches the last rof_aggregate() on this thread enqueued. */
+int rof_last_launch_count(void);
+
+/* Message for the last non-OK status returned on this thread (never NULL). */
+const char* rof_last_error(void);
+
+/* Library version, and the compute capability the kernels were compiled for (100). */
+int rof_version(void);
+int rof_compiled_arch(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ROF_B200_H_ */

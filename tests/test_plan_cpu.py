@@ -1,0 +1,131 @@
+"""Plan builder (host part of the CUDA library) on the fixtures: the destination-major plan
+must expand back to exactly the original CSR, for all three layouts; bad layouts are
+rejected with a status, not a crash.  Runs without a GPU (host-only plans)."""
+import numpy as np
+import pytest
+
+from artifact_b200 import _native
+from artifact_b200.plan import AggregationPlan
+from conftest import layout_args
+
+BUILDERS = {"parts": AggregationPlan.from_parts, "v1": AggregationPlan.from_v1, "v2": AggregationPlan.from_v2}
+
+
+def expand_rows(ex, N):
+    rows = []
+    for r in range(len(ex["row_ptr"]) - 1):
+        ent = ex["col"][ex["row_ptr"][r]:ex["row_ptr"][r + 1]]
+        src = []
+        for c in ent:
+            if c < N:
+                src.append(int(c))
+            else:
+                g = c - N
+                src.extend(int(s) for s in ex["group_col"][ex["group_ptr"][g]:ex["group_ptr"][g + 1]])
+        rows.append(sorted(src))
+    return rows
+
+
+@pytest.mark.parametrize("which", ["parts", "v1", "v2"])
+def test_plan_round_trip(golden, which):
+    N = golden["N"]
+    plan = BUILDERS[which](N, *layout_args(golden["layouts"], which))
+    ex = plan.export()
+    rows = expand_rows(ex, N)
+    ip, ix = golden["indptr_dst"], golden["indices_src"]
+    for v in range(N):
+        assert rows[v] == list(ix[ip[v]:ip[v + 1]]), (which, v)
+    info = plan.info
+    assert info["original_edges"] == len(ix)
+    assert info["gather_entries"] == len(ex["col"])
+    # the reuse accounting of upstream's scripts (small-main.py:176-188): every group saves
+    # (fan-out - 1) * part_size gathered rows and costs fan-out partial rows
+    if which != "parts":
+        fan = golden["layouts"]["picked_fanout"].astype(np.int64)
+        ps = golden["layouts"]["part_size"]
+        assert info["num_groups"] == len(fan)
+        assert info["partial_entries"] == fan.sum()
+        assert info["gather_entries"] == len(ix) - ps * fan.sum() + fan.sum()
+        assert info["group_sources"] == ps * len(fan)
+
+
+@pytest.mark.parametrize("which", ["parts", "v2"])
+def test_items_cover_every_entry_once(golden, which):
+    N = golden["N"]
+    plan = BUILDERS[which](N, *layout_args(golden["layouts"], which))
+    ex = plan.export()
+    covered = np.zeros(len(ex["col"]), np.int32)
+    seen_rows = set()
+    lens = []
+    for b, e, dst, _ in ex["items"]:
+        covered[b:e] += 1
+        lens.append(e - b)
+        assert e - b <= plan.info["segment_edges"]
+        if dst >= 0:
+            assert dst not in seen_rows
+            seen_rows.add(int(dst))
+            assert (b, e) == (ex["row_ptr"][dst], ex["row_ptr"][dst + 1])
+    assert (covered == 1).all()
+    assert lens == sorted(lens, reverse=True)            # longest first
+    split = {int(r) for r, _, _, _ in ex["split_rows"]}
+    assert seen_rows | split == set(range(N)) and not (seen_rows & split)
+    for row, first, count, _ in ex["split_rows"]:
+        segs = sorted((b, e) for b, e, dst, _ in ex["items"] if dst < 0 and first <= -dst - 1 < first + count)
+        assert segs[0][0] == ex["row_ptr"][row] and segs[-1][1] == ex["row_ptr"][row + 1]
+        assert all(a[1] == b[0] for a, b in zip(segs, segs[1:]))
+
+
+def test_row_block_plans_tile_the_graph(golden):
+    N = golden["N"]
+    L = golden["layouts"]
+    full = AggregationPlan.from_v2(N, *layout_args(L, "v2")).export()
+    full_rows = expand_rows(full, N)
+    cuts = [0, N // 3, N // 3, (2 * N) // 3, N]
+    got = []
+    for r0, r1 in zip(cuts[:-1], cuts[1:]):
+        p = AggregationPlan.from_v2(N, *layout_args(L, "v2"), rows=(r0, r1))
+        assert (p.info["row_begin"], p.info["row_end"]) == (r0, r1)
+        got += expand_rows(p.export(), N)
+    assert got == full_rows
+
+
+def test_empty_graph_and_no_groups():
+    z = np.zeros(0, np.int32)
+    p = AggregationPlan.from_parts(0, z, z, z)
+    assert p.info["num_items"] == 0
+    p = AggregationPlan.from_v1(5, np.array([1, 2], np.int32), np.array([0, 2], np.int32), np.array([3], np.int32),
+                                np.array([0], np.int32), np.array([0], np.int32), z)
+    assert p.info["num_groups"] == 0 and p.info["num_items"] == 5
+    assert p.workspace_bytes(64) == 0
+
+
+@pytest.mark.parametrize("case", ["col_range", "ptr_order", "dst_range", "flag_range", "ptr_overrun"])
+def test_bad_layouts_are_rejected(case):
+    col = np.array([0, 1, 2, 3], np.int32)
+    pp = np.array([0, 2, 4], np.int32)
+    p2n = np.array([1, 2], np.int32)
+    flag = np.array([0, 0], np.int32)
+    ppc = np.array([0, 2], np.int32)
+    cic = np.array([0, 1], np.int32)
+    if case == "col_range":
+        col = np.array([0, 1, 9, 3], np.int32)
+    elif case == "ptr_order":
+        pp = np.array([0, 3, 2], np.int32)
+    elif case == "dst_range":
+        p2n = np.array([1, -1], np.int32)
+    elif case == "flag_range":
+        flag = np.array([0, 2], np.int32)
+    elif case == "ptr_overrun":
+        pp = np.array([0, 2, 5], np.int32)
+    with pytest.raises(_native.RofError) as e:
+        AggregationPlan.from_v1(4, col, pp, p2n, flag, ppc, cic)
+    assert e.value.status == 2 and "bad layout" in str(e.value)
+
+
+def test_bad_arguments():
+    z = np.zeros(0, np.int32)
+    with pytest.raises(_native.RofError) as e:
+        AggregationPlan.from_parts(4, z, z, z, rows=(3, 2))
+    assert e.value.status == 1
+    with pytest.raises(TypeError):
+        AggregationPlan.from_parts(4, np.zeros(2, np.float32), z, z)
