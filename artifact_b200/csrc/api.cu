@@ -64,7 +64,8 @@ int rof_aggregate_phases(const rof_plan* p, int phases, int mode, const float* x
                          const float* degrees, float* out, int64_t ldo, float* cache_result,
                          void* workspace, int64_t workspace_bytes, void* stream_) {
   g_last_launches = 0;
-  if (phases & ~ROF_PHASE_ALL) { set_error("rof_aggregate_phases: unknown phase bit"); return ROF_ERR_BAD_ARGUMENT; }
+  if (phases & ~(ROF_PHASE_ALL | ROF_PHASE_ACCUMULATE)) { set_error("rof_aggregate_phases: unknown phase bit"); return ROF_ERR_BAD_ARGUMENT; }
+  const int accumulate = (phases & ROF_PHASE_ACCUMULATE) ? 1 : 0;
   cudaStream_t stream = (cudaStream_t)stream_;
   if (p == nullptr) { set_error("rof_aggregate: null plan"); return ROF_ERR_BAD_ARGUMENT; }
   if (mode != ROF_MODE_GCN && mode != ROF_MODE_SUM && mode != ROF_MODE_MEAN) { set_error("rof_aggregate: unknown mode"); return ROF_ERR_BAD_ARGUMENT; }
@@ -112,6 +113,7 @@ int rof_aggregate_phases(const rof_plan* p, int phases, int mode, const float* x
     a.out = out; a.ldo = ldo; a.slots = slots; a.lds = w.ld;
     a.mirror = nullptr; a.ldm = 0; a.mirror_flag_col = -1;
     a.num_nodes = p->num_nodes; a.row_begin = p->row_begin; a.dim = dim; a.weight_gcn = gcn; a.scale_mode = scale_mode;
+    a.accumulate = accumulate;
     e = launch_gather(a, stream);
     if (e != cudaSuccess) return cuda_fail(e, "phase B (destination gather)");
     g_last_launches += (dim + 2047) / 2048;
@@ -120,6 +122,7 @@ int rof_aggregate_phases(const rof_plan* p, int phases, int mode, const float* x
     ReduceArgs r{};
     r.rows = p->d_split; r.num_rows = p->num_split_rows; r.slots = slots; r.lds = w.ld; r.degrees = degrees;
     r.out = out; r.ldo = ldo; r.row_begin = p->row_begin; r.dim = dim; r.scale_mode = scale_mode;
+    r.accumulate = accumulate;
     e = launch_split_reduce(r, stream);
     if (e != cudaSuccess) return cuda_fail(e, "segment reduce");
     g_last_launches += 1;

@@ -10,17 +10,20 @@
 // atomics and no zero-fill pass (upstream: atomicAdd_F per element per part and a
 // torch::zeros per call, reuse_conv_kernel.cu:16-21, 282, 303).
 //
-// Arithmetic per term is upstream's: an un-fused multiply by rsqrt(degrees[src]) rounded to
-// nearest, then an add (reuse_conv_kernel.cu:254, 270); the file is compiled with -fmad=false.
+// The kernel is bound by instruction issue before it is bound by L2 or HBM (hub rows are
+// re-read from L2), so the inner loop is kept to one shuffle, one 64-bit multiply-add and
+// the loads and adds per entry: an item's entries are ordered [partial rows | feature rows]
+// so each range has a fixed base pointer, the unweighted modes (sum, mean, partial rows) do
+// no multiply at all, and full batches run without per-entry predicates.
+//
+// Arithmetic: sum/mean add the gathered values (rounded to nearest); GCN adds
+// rsqrt_rn(degrees[src]) * x with one fused multiply-add per term — a single rounding where
+// upstream has two (__fmul_rn then add, reuse_conv_kernel.cu:254, 270); the order of the adds
+// differs from upstream's (arbitrary atomic order) in any case.
 #include "rof_internal.h"
 
 namespace rof {
 namespace {
-
-template <int VEC> struct Vec;
-template <> struct Vec<4> { using type = float4; };
-template <> struct Vec<2> { using type = float2; };
-template <> struct Vec<1> { using type = float; };
 
 template <int VEC>
 __device__ __forceinline__ void load_row_vec(float (&v)[VEC], const float* p) {
@@ -46,49 +49,35 @@ __device__ __forceinline__ void store_row_vec(float* p, const float (&v)[VEC]) {
   }
 }
 
-// VEC floats per load, L lanes per item, C vectors per lane (L*C*VEC >= dim), U rows in flight.
-template <int VEC, int L, int C, int U>
-__global__ void __launch_bounds__(256) gather_rows_kernel(const GatherArgs a) {
-  static_assert(U <= L, "a batch of L entries must cover one unrolled step");
-  const int64_t gtid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  const int item_id = (int)(gtid / L);
-  if (item_id >= a.num_items) return;  // whole lane groups leave together
-  const int lane = threadIdx.x & (L - 1);
-  const unsigned gmask = (L == 32) ? 0xffffffffu : (((1u << L) - 1u) << ((threadIdx.x & 31) & ~(L - 1)));
-
-  const int4 raw = __ldg(reinterpret_cast<const int4*>(a.items) + item_id);
-  const int begin = raw.x, end = raw.y, dst = raw.z;
-  const int nvec = a.dim / VEC;
-  const int n_nodes = a.num_nodes;
-
-  float acc[C][VEC];
-#pragma unroll
-  for (int k = 0; k < C; ++k)
-#pragma unroll
-    for (int t = 0; t < VEC; ++t) acc[k][t] = 0.0f;
-
+// acc += sum over col[begin, end) of (WEIGHTED ? rsqrt(degrees[c]) : 1) * row(c), where
+// row(c) starts at base_lane + (c - c_offset) * ld (base_lane already includes this lane's
+// column offset).  `active[k]` says whether this lane's k-th vector lies inside the row.
+template <int VEC, int L, int C, int U, bool WEIGHTED>
+__device__ __forceinline__ void accumulate_range(float (&acc)[C][VEC], const int32_t* __restrict__ col, int begin,
+                                                 int end, const float* base_lane, int64_t ld, int c_offset,
+                                                 const float* __restrict__ degrees, int lane, unsigned gmask,
+                                                 const bool (&active)[C]) {
   for (int e = begin; e < end; e += L) {
     const int mine = e + lane;
     int c = 0;
     float w = 1.0f;
     if (mine < end) {
-      c = __ldg(a.col + mine);
-      if (a.weight_gcn && c < n_nodes) w = __frsqrt_rn(__ldg(a.degrees + c));
+      c = __ldg(col + mine);
+      if constexpr (WEIGHTED) w = __frsqrt_rn(__ldg(degrees + c));
+      c -= c_offset;
     }
     const int cnt = min(L, end - e);
-    for (int j = 0; j < cnt; j += U) {
+    int j = 0;
+    for (; j + U <= cnt; j += U) {  // full batches: no per-entry predicate
       float v[U][C][VEC];
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int cj = __shfl_sync(gmask, c, j + u, L);
-        const bool ok = (j + u) < cnt;
-        const float* rp = (cj < n_nodes) ? a.x + (int64_t)cj * a.ldx
-                                         : a.partials + (int64_t)(cj - n_nodes) * a.ldp;
+        const float* rp = base_lane + (int64_t)cj * ld;
 #pragma unroll
         for (int k = 0; k < C; ++k) {
-          const int iv = lane + k * L;
-          if (ok && iv < nvec) {
-            load_row_vec<VEC>(v[u][k], rp + (int64_t)iv * VEC);
+          if (active[k]) {
+            load_row_vec<VEC>(v[u][k], rp + k * (L * VEC));
           } else {
 #pragma unroll
             for (int t = 0; t < VEC; ++t) v[u][k][t] = 0.0f;
@@ -97,16 +86,82 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const GatherArgs a) {
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const float wj = __shfl_sync(gmask, w, j + u, L);
+        float wj = 1.0f;
+        if constexpr (WEIGHTED) wj = __shfl_sync(gmask, w, j + u, L);
+#pragma unroll
+        for (int k = 0; k < C; ++k)
+#pragma unroll
+          for (int t = 0; t < VEC; ++t) {
+            if constexpr (WEIGHTED) acc[k][t] = __fmaf_rn(wj, v[u][k][t], acc[k][t]);
+            else acc[k][t] = __fadd_rn(acc[k][t], v[u][k][t]);
+          }
+      }
+    }
+    if (j < cnt) {  // the last, partial batch of the range: same shape, predicated per entry
+      float v[U][C][VEC];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int cj = __shfl_sync(gmask, c, j + u, L);
+        const bool ok = (j + u) < cnt;
+        const float* rp = base_lane + (int64_t)cj * ld;
+#pragma unroll
+        for (int k = 0; k < C; ++k) {
+          if (ok && active[k]) {
+            load_row_vec<VEC>(v[u][k], rp + k * (L * VEC));
+          } else {
+#pragma unroll
+            for (int t = 0; t < VEC; ++t) v[u][k][t] = 0.0f;
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float wj = 1.0f;
+        if constexpr (WEIGHTED) wj = __shfl_sync(gmask, w, j + u, L);
         if ((j + u) < cnt) {
 #pragma unroll
           for (int k = 0; k < C; ++k)
 #pragma unroll
-            for (int t = 0; t < VEC; ++t) acc[k][t] = __fadd_rn(acc[k][t], __fmul_rn(wj, v[u][k][t]));
+            for (int t = 0; t < VEC; ++t) {
+              if constexpr (WEIGHTED) acc[k][t] = __fmaf_rn(wj, v[u][k][t], acc[k][t]);
+              else acc[k][t] = __fadd_rn(acc[k][t], v[u][k][t]);
+            }
         }
       }
     }
   }
+}
+
+// VEC floats per load, L lanes per item, C vectors per lane (L*C*VEC >= dim), U rows in flight;
+// WEIGHTED: multiply each feature row by rsqrt(degrees[col]) (GCN).
+template <int VEC, int L, int C, int U, bool WEIGHTED>
+__global__ void __launch_bounds__(256, (C <= 2 ? 4 : 1)) gather_rows_kernel(const GatherArgs a) {
+  static_assert(U <= L && (L % U) == 0, "a batch of L entries is a whole number of unrolled steps");
+  const int64_t gtid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int item_id = (int)(gtid / L);
+  if (item_id >= a.num_items) return;  // whole lane groups leave together
+  const int lane = threadIdx.x & (L - 1);
+  const unsigned gmask = (L == 32) ? 0xffffffffu : (((1u << L) - 1u) << ((threadIdx.x & 31) & ~(L - 1)));
+
+  const int4 raw = __ldg(reinterpret_cast<const int4*>(a.items) + item_id);
+  const int begin = raw.x, end = raw.y, dst = raw.z, mid = raw.w;  // [begin,mid) partial rows, [mid,end) feature rows
+  const int nvec = a.dim / VEC;
+
+  bool active[C];
+  float acc[C][VEC];
+#pragma unroll
+  for (int k = 0; k < C; ++k) {
+    active[k] = (lane + k * L) < nvec;
+#pragma unroll
+    for (int t = 0; t < VEC; ++t) acc[k][t] = 0.0f;
+  }
+
+  if (mid > begin)
+    accumulate_range<VEC, L, C, U, false>(acc, a.col, begin, mid, a.partials + lane * VEC, a.ldp, a.num_nodes,
+                                          nullptr, lane, gmask, active);
+  if (end > mid)
+    accumulate_range<VEC, L, C, U, WEIGHTED>(acc, a.col, mid, end, a.x + lane * VEC, a.ldx, 0, a.degrees, lane,
+                                             gmask, active);
 
   float scale = 1.0f;
   float* op;
@@ -127,11 +182,16 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const GatherArgs a) {
   }
 #pragma unroll
   for (int k = 0; k < C; ++k) {
-    const int iv = lane + k * L;
-    if (iv < nvec) {
+    if (active[k]) {
+      const int iv = lane + k * L;
       float r[VEC];
 #pragma unroll
       for (int t = 0; t < VEC; ++t) r[t] = __fmul_rn(acc[k][t], scale);
+      if (a.accumulate && dst >= 0) {  // a later stage of a staged pass adds to the row
+        const float* prev = op + (int64_t)iv * VEC;
+#pragma unroll
+        for (int t = 0; t < VEC; ++t) r[t] = __fadd_rn(prev[t], r[t]);
+      }
       store_row_vec<VEC>(op + (int64_t)iv * VEC, r);
       if (a.mirror != nullptr && dst >= 0) {
         float* mp = a.mirror + (int64_t)dst * a.ldm + (int64_t)iv * VEC;
@@ -162,7 +222,8 @@ __global__ void __launch_bounds__(256) split_reduce_kernel(const ReduceArgs a) {
   for (int d = lane; d < a.dim; d += 32) {
     float s = 0.0f;
     for (int k = 0; k < count; ++k) s = __fadd_rn(s, a.slots[(int64_t)(first + k) * a.lds + d]);
-    op[d] = __fmul_rn(s, scale);
+    const float r = __fmul_rn(s, scale);
+    op[d] = a.accumulate ? __fadd_rn(op[d], r) : r;
   }
 }
 
@@ -172,7 +233,10 @@ cudaError_t launch_one(const GatherArgs& a, cudaStream_t stream) {
   const int64_t total = (int64_t)a.num_items * L;
   const int64_t blocks = (total + threads - 1) / threads;
   if (blocks > 0x7fffffffLL) return cudaErrorInvalidConfiguration;
-  gather_rows_kernel<VEC, L, C, U><<<(unsigned)blocks, threads, 0, stream>>>(a);
+  if (a.weight_gcn)
+    gather_rows_kernel<VEC, L, C, U, true><<<(unsigned)blocks, threads, 0, stream>>>(a);
+  else
+    gather_rows_kernel<VEC, L, C, U, false><<<(unsigned)blocks, threads, 0, stream>>>(a);
   return cudaGetLastError();
 }
 

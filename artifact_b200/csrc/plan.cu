@@ -92,7 +92,7 @@ int sync_if_device(int where, cudaStream_t stream) {
 // ---------------------------------------------------------------------------------------
 // finalize: row lists -> sorted work items -> device
 // ---------------------------------------------------------------------------------------
-int finalize_plan(const HostPlan& hp, rof_plan** out, cudaStream_t stream) {
+int finalize_plan(HostPlan& hp, rof_plan** out, cudaStream_t stream) {
   const int rows = hp.row_end - hp.row_begin;
   const int64_t entries = (int64_t)hp.col.size();
   const int64_t gsrc = (int64_t)hp.group_col.size();
@@ -117,7 +117,16 @@ int finalize_plan(const HostPlan& hp, rof_plan** out, cudaStream_t stream) {
   p->group_sources = gsrc;
   p->gather_entries = entries;
   p->original_edges = hp.original_edges;
-  for (int32_t c : hp.col) p->partial_entries += (c >= hp.num_nodes);
+  // Every row lists its partial rows first, then its feature rows (the order the v1 / v2
+  // layouts already produce), so the kernel walks two ranges with one base pointer each.
+  std::vector<int64_t> row_mid((size_t)rows);
+  const int32_t n_nodes = hp.num_nodes;
+#pragma omp parallel for schedule(static, 1024)
+  for (int r = 0; r < rows; ++r) {
+    auto b = hp.col.begin() + hp.row_ptr[r], e = hp.col.begin() + hp.row_ptr[r + 1];
+    row_mid[(size_t)r] = std::stable_partition(b, e, [n_nodes](int32_t c) { return c >= n_nodes; }) - hp.col.begin();
+  }
+  for (int r = 0; r < rows; ++r) p->partial_entries += row_mid[(size_t)r] - hp.row_ptr[r];
 
   // rows ordered by length, longest first (stable: equal lengths keep ascending row id)
   std::vector<int32_t> order((size_t)rows);
@@ -134,14 +143,15 @@ int finalize_plan(const HostPlan& hp, rof_plan** out, cudaStream_t stream) {
     const int64_t b = hp.row_ptr[r], en = hp.row_ptr[r + 1];
     const int64_t len = en - b;
     if (len <= kSegmentEdges) {
-      items.push_back(WorkItem{(int32_t)b, (int32_t)en, hp.row_begin + r, 0});
+      items.push_back(WorkItem{(int32_t)b, (int32_t)en, hp.row_begin + r, (int32_t)row_mid[(size_t)r]});
     } else {
       const int nseg = (int)((len + kSegmentEdges - 1) / kSegmentEdges);
       split.push_back(SplitRow{hp.row_begin + r, slots, nseg, 0});
       for (int s = 0; s < nseg; ++s) {
         const int64_t sb = b + (int64_t)s * kSegmentEdges;
         const int64_t se = std::min(en, sb + kSegmentEdges);
-        items.push_back(WorkItem{(int32_t)sb, (int32_t)se, -(slots + s) - 1, 0});
+        const int64_t sm = std::min(se, std::max(sb, row_mid[(size_t)r]));
+        items.push_back(WorkItem{(int32_t)sb, (int32_t)se, -(slots + s) - 1, (int32_t)sm});
       }
       slots += nseg;
     }
@@ -155,7 +165,8 @@ int finalize_plan(const HostPlan& hp, rof_plan** out, cudaStream_t stream) {
 
   std::vector<WorkItem> gitems((size_t)p->num_groups);
   for (int g = 0; g < p->num_groups; ++g)
-    gitems[g] = WorkItem{(int32_t)(entries + hp.group_ptr[g]), (int32_t)(entries + hp.group_ptr[g + 1]), g, 0};
+    gitems[g] = WorkItem{(int32_t)(entries + hp.group_ptr[g]), (int32_t)(entries + hp.group_ptr[g + 1]), g,
+                         (int32_t)(entries + hp.group_ptr[g])};
 
   p->h_row_ptr = hp.row_ptr;
   p->h_group_ptr = hp.group_ptr;

@@ -17,7 +17,7 @@ struct __align__(16) WorkItem {
   int32_t begin;
   int32_t end;
   int32_t dst;
-  int32_t pad;
+  int32_t mid;   // entries [begin, mid) name partial rows, [mid, end) feature rows
 };
 
 // Second-stage reduce of a split row: out[row] = scale * (slot[first] + ... + slot[first+count-1]).
@@ -78,7 +78,7 @@ struct HostPlan {
   int64_t original_edges = 0;
 };
 
-int finalize_plan(const HostPlan& hp, rof_plan** out, cudaStream_t stream);
+int finalize_plan(HostPlan& hp, rof_plan** out, cudaStream_t stream);
 
 struct GatherArgs {
   const WorkItem* items;
@@ -96,6 +96,7 @@ struct GatherArgs {
   int dim;
   int weight_gcn;   // multiply each feature row by rsqrt(degrees[col])
   int scale_mode;   // 0 none, 1 rsqrt(degrees[dst]), 2 1/degrees[dst]
+  int accumulate;   // dst >= 0 rows: out += result instead of out = result
 };
 
 struct ReduceArgs {
@@ -107,6 +108,7 @@ struct ReduceArgs {
   int row_begin;
   int dim;
   int scale_mode;
+  int accumulate;
 };
 
 // Launchers (kernels.cu).  Return cudaSuccess or the launch error.

@@ -120,6 +120,20 @@ class AggregationPlan:
                 cls._stream(device)))
         return cls(h, "v2", device, keep)
 
+    def stages(self, block_rows, stage_of_block):
+        """Split this plan for the multi-GPU pipeline (rof_plan_create_stages): feature block b
+        (rows [b*block_rows, (b+1)*block_rows)) becomes readable in stage stage_of_block[b].
+        Returns the list of per-stage plans; run them in order, all but the first with
+        accumulate=True."""
+        sob = np.ascontiguousarray(stage_of_block, dtype=np.int32)
+        num_stages = int(sob.max()) + 1 if sob.size else 1
+        handles = (ctypes.c_void_p * num_stages)()
+        with _device_guard(self.device):
+            _native.check(_native.cuda().rof_plan_create_stages(
+                self._h, int(block_rows), ctypes.c_void_p(sob.ctypes.data), int(sob.size), num_stages, handles,
+                self._stream(self.device)))
+        return [AggregationPlan(ctypes.c_void_p(h), self.layout + ":stage", self.device, self._keep) for h in handles]
+
     # -- inspection --------------------------------------------------------------------
     def export(self):
         i = self.info
@@ -149,7 +163,8 @@ class AggregationPlan:
             self._workspace = ws
         return ws
 
-    def aggregate(self, x, degrees=None, mode="gcn", out=None, cache_result=None, workspace=None, phases=7):
+    def aggregate(self, x, degrees=None, mode="gcn", out=None, cache_result=None, workspace=None, phases=7,
+                  accumulate=False):
         """out[v] = scale(v) * sum over v's gathered rows; see rof_aggregate() in include/rof_b200.h.
         `x` is [num_nodes, dim] fp32 on the GPU; returns a new [rows, dim] tensor unless `out` is given."""
         if not x.is_cuda:
@@ -164,6 +179,8 @@ class AggregationPlan:
         dim = x.size(1)
         rows = i["row_end"] - i["row_begin"]
         if out is None:
+            if accumulate:
+                raise RuntimeError("accumulate=True adds to an existing `out`")
             out = torch.empty((rows, dim), dtype=torch.float32, device=x.device)
         elif (out.dtype != torch.float32 or not out.is_cuda or out.dim() != 2 or out.size(0) != rows
               or out.size(1) != dim or (out.stride(1) != 1 and dim > 1)):
@@ -190,7 +207,7 @@ class AggregationPlan:
         with _device_guard(x.device):
             stream = ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
             _native.check(_native.cuda().rof_aggregate_phases(
-                self._h, int(phases), m, ctypes.c_void_p(x.data_ptr()), ldx, dim, deg_ptr, ctypes.c_void_p(out.data_ptr()), ldo,
+                self._h, int(phases) | (8 if accumulate else 0), m, ctypes.c_void_p(x.data_ptr()), ldx, dim, deg_ptr, ctypes.c_void_p(out.data_ptr()), ldo,
                 cache_ptr, ctypes.c_void_p(ws.data_ptr()) if ws is not None else None,
                 ws.numel() if ws is not None else 0, stream))
         return out

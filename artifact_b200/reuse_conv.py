@@ -33,6 +33,9 @@ class ROF_GCNConvFunc(torch.autograd.Function):
         ctx.kernel_type = kernel_type
         ctx.launch = (info.partSize, info.dimWorker, info.warpPerBlock)
         ctx.info = info
+        # the layer rebinds inputInfo.part_result_cache on every call (one buffer per layer), so the
+        # one seen now is the one backward must use (upstream saves it with save_for_backward)
+        ctx.cache = info.part_result_cache
         ctx.save_for_backward(x, weight)
         ps, dw, wpb = ctx.launch
         if kernel_type == "GNNA":
@@ -58,7 +61,7 @@ class ROF_GCNConvFunc(torch.autograd.Function):
         elif ctx.kernel_type == "ROF_v1":
             d_input, d_weight = ROF.reuse_backward_v1(grad_output, x, weight, info.column_index, info.degrees,
                                                       info.part_pointers, info.part2Node, ps, dw, wpb,
-                                                      info.part_result_cache, info.part_cache_flagindex,
+                                                      ctx.cache, info.part_cache_flagindex,
                                                       info.part_pointers_cache, info.column_index_cache)
         else:
             d_input, d_weight = ROF.reuse_backward_v2(grad_output, x, weight, info.uniqpart_column_index,

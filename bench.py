@@ -35,6 +35,14 @@ WORKLOADS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one phase-B launch, from the ncu captures
+# summarised in profiles/gather_rows_<workload>_d<D>_<mode>.md (captured once per kernel change)
+NCU_DRAM_BYTES_PER_LAUNCH = {
+    "c2:D256:sum": 25.03e9,
+    "c2:D64:sum": 1.44e9,
+}
+
+
 def load_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
@@ -220,7 +228,9 @@ def workload_config(args, g, ratios):
                      f"D={args.dim}, {args.mode} aggregation, forward+backward pass per step",
          "part_size": args.part_size, "layout": "ROF_v2", "scale": args.scale,
          "l2": "feature matrix and index arrays together exceed L2 (126 MB); no flush between iterations",
-         "parallelism": f"row-block x{args.gpus}" if args.gpus > 1 else "single GPU"}
+         "parallelism": (f"row-block x{args.gpus}, " + ("all-gather rounds overlapped with staged aggregation"
+                                                        if args.pipeline else "all-gather then aggregate"))
+         if args.gpus > 1 else "single GPU"}
     if ratios is not None:
         c["reuse"] = ratios
     return c
@@ -238,6 +248,8 @@ def main():
     ap.add_argument("--part-size", type=int, default=0)
     ap.add_argument("--mode", default="")
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (tests / profiling only)")
+    ap.add_argument("--no-pipeline", dest="pipeline", action="store_false",
+                    help="N > 1: one all-gather, then the aggregation (no overlap)")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--only-kernel", action="store_true", help="skip sweep, CPU baseline and e2e (profiling)")
@@ -290,22 +302,30 @@ def main():
     my_edges = int(g.indptr_dst[r1] - g.indptr_dst[r0])
     deg = torch.from_numpy(np.maximum(g.degrees_f32(), 1.0)).to(dev)
 
+    from artifact_b200.sharding import PipelinedAggregator, ShardedFeatures
     gen = torch.Generator(device=dev); gen.manual_seed(1234)
-    x_full = torch.empty((n_pad, D), device=dev)
-    g_full = torch.empty((n_pad, D), device=dev)
-    x_full.normal_(generator=gen); g_full.normal_(generator=gen)
-    x_loc = x_full[rank * blk:(rank + 1) * blk].clone()
-    g_loc = g_full[rank * blk:(rank + 1) * blk].clone()
+    feat_x = ShardedFeatures(n, D, rank, world, dev)
+    feat_g = ShardedFeatures(n, D, rank, world, dev)
+    feat_x.full.normal_(generator=gen); feat_g.full.normal_(generator=gen)
+    x_loc = feat_x.local_view().clone()
+    g_loc = feat_g.local_view().clone()
     out_f = torch.empty((r1 - r0, D), device=dev)
     out_b = torch.empty((r1 - r0, D), device=dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)
     gather_events = []
     launches = [0]
+    pipes = {}
+    if world > 1 and args.pipeline:
+        px = PipelinedAggregator(plan, feat_x)
+        pipes = {id(feat_x): px, id(feat_g): PipelinedAggregator(plan, feat_g, stage_plans=px.stage_plans)}
 
-    def one_pass(p, src_loc, src_full, out, timed_gather=False):
-        if world > 1:
-            dist.all_gather_into_tensor(src_full, src_loc)
-        xs = src_full[:n]
+    def one_pass(p, src_loc, feat, out, timed_gather=False):
+        if pipes and p is plan:       # all-gather rounds overlapped with the per-stage aggregation
+            pipe = pipes[id(feat)]
+            pipe.aggregate(src_loc, deg, mode, out)
+            launches[0] += pipe.launches
+            return
+        xs = feat.all_gather(src_loc) if world > 1 else feat.full[:n]
         if timed_gather:
             p.aggregate(xs, deg, mode, out=out, phases=1); launches[0] += p.last_launch_count()
             e0, e1 = ev(), ev()
@@ -318,8 +338,8 @@ def main():
             p.aggregate(xs, deg, mode, out=out); launches[0] += p.last_launch_count()
 
     def step(p, timed_gather=False):
-        one_pass(p, x_loc, x_full, out_f, timed_gather)
-        one_pass(p, g_loc, g_full, out_b, timed_gather)
+        one_pass(p, x_loc, feat_x, out_f, timed_gather)
+        one_pass(p, g_loc, feat_g, out_b, timed_gather)
 
     def timed(p, steps, warmup, timed_gather=False):
         for _ in range(warmup):
@@ -355,6 +375,14 @@ def main():
     value = 2.0 * E / (ms_step / 1e3)
 
     # dominant kernel: the phase-B gather of this rank's block, timed by events inside the steps
+    if not gather_events:             # pipelined run: time this rank's whole-block gather kernel on its own
+        xs = feat_x.full[:n]
+        for i in range(8):
+            e0, e1 = ev(), ev()
+            e0.record(); plan.aggregate(xs, deg, mode, out=out_f, phases=2); e1.record()
+            if i >= 3:
+                gather_events.append((e0, e1))
+        torch.cuda.synchronize()
     gms = float(np.mean([a.elapsed_time(b) for a, b in gather_events]))
     info = plan.info
     row_b = 4.0 * D
@@ -367,17 +395,11 @@ def main():
                 "algorithmic_bytes_per_launch": gather_bytes, "peak_kind": f"{peak_kind} copy bandwidth",
                 "note": "algorithmic bytes = (gathered rows + written rows) x 4D + 4 per index; hub rows are "
                         "re-read from L2, so achieved can exceed the DRAM peak; see profiles/ for DRAM traffic"}
-    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(traffic_file):
-        try:
-            t = json.load(open(traffic_file)).get(f"{args.workload}:D{D}:{mode}")
-            if t and world == 1 and args.scale == 1.0:
-                roofline["traffic"] = t["dram_bytes_per_launch"]
-        except Exception:
-            pass
+    if world == 1 and args.scale == 1.0 and args.part_size == WORKLOADS[args.workload][2]:
+        roofline["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(f"{args.workload}:D{D}:{mode}")
 
     extra = {}
-    if world == 1:
+    if world == 1 and not args.only_kernel:
         ms_plain, _, _ = timed(plain, max(3, args.steps // 2), 3)
         extra["plain"] = {"ms_per_step": ms_plain, "edges_per_s": 2.0 * E / (ms_plain / 1e3),
                           "algorithmic_GBs": 2 * plain.algorithmic_bytes(D, mode) / ms_plain / 1e6}
@@ -385,39 +407,43 @@ def main():
                           "algorithmic_GBs": 2 * plan.algorithmic_bytes(D, mode) / ms_step / 1e6}
 
     # ---- end to end through the public API with host buffers -----------------------------------
-    h_x = torch.empty((blk, D), pin_memory=True); h_x.copy_(x_loc)
-    h_g = torch.empty((blk, D), pin_memory=True); h_g.copy_(g_loc)
-    h_of = torch.empty((r1 - r0, D), pin_memory=True)
-    h_ob = torch.empty((r1 - r0, D), pin_memory=True)
+    def measure_e2e():
+        h_x = torch.empty((blk, D), pin_memory=True); h_x.copy_(x_loc)
+        h_g = torch.empty((blk, D), pin_memory=True); h_g.copy_(g_loc)
+        h_of = torch.empty((r1 - r0, D), pin_memory=True)
+        h_ob = torch.empty((r1 - r0, D), pin_memory=True)
 
-    def e2e_step():
-        x_loc.copy_(h_x, non_blocking=True)
-        one_pass(plan, x_loc, x_full, out_f)
-        h_of.copy_(out_f, non_blocking=True)
-        g_loc.copy_(h_g, non_blocking=True)
-        one_pass(plan, g_loc, g_full, out_b)
-        h_ob.copy_(out_b, non_blocking=True)
+        def e2e_step():
+            x_loc.copy_(h_x, non_blocking=True)
+            one_pass(plan, x_loc, feat_x, out_f)
+            h_of.copy_(out_f, non_blocking=True)
+            g_loc.copy_(h_g, non_blocking=True)
+            one_pass(plan, g_loc, feat_g, out_b)
+            h_ob.copy_(out_b, non_blocking=True)
 
-    e2e_steps = max(3, min(args.steps, 10))
-    for _ in range(3):
-        e2e_step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    s, e = ev(), ev()
-    s.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e.record()
-    torch.cuda.synchronize()
-    ms_e2e = torch.tensor([s.elapsed_time(e) / e2e_steps], device=dev)
-    if world > 1:
-        dist.all_reduce(ms_e2e, op=dist.ReduceOp.MAX)
-    ms_e2e = float(ms_e2e.item())
-    e2e = {"value": 2.0 * E / (ms_e2e / 1e3), "unit": "edges/s", "ms_per_step": ms_e2e,
-           "h2d_bytes_per_step": 2 * blk * D * 4 * world, "d2h_bytes_per_step": 2 * n * D * 4,
-           "note": "features and gradients copied from pinned host memory, both results copied back, every step; "
-                   "the graph plan stays resident like upstream's inputInfo tensors"}
+        e2e_steps = max(3, min(args.steps, 10))
+        for _ in range(3):
+            e2e_step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        s, e = ev(), ev()
+        s.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e.record()
+        torch.cuda.synchronize()
+        ms_e2e = torch.tensor([s.elapsed_time(e) / e2e_steps], device=dev)
+        if world > 1:
+            dist.all_reduce(ms_e2e, op=dist.ReduceOp.MAX)
+        ms_e2e = float(ms_e2e.item())
+        e2e = {"value": 2.0 * E / (ms_e2e / 1e3), "unit": "edges/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": 2 * blk * D * 4 * world, "d2h_bytes_per_step": 2 * n * D * 4,
+               "note": "features and gradients copied from pinned host memory, both results copied back, every step; "
+                       "the graph plan stays resident like upstream's inputInfo tensors"}
+        return e2e
+
+    e2e = None if args.only_kernel else measure_e2e()
 
     # ---- width / mode sweep (single GPU only; informational) -----------------------------------
     if world == 1 and not args.no_sweep:

@@ -109,12 +109,26 @@ int rof_plan_get_info(const rof_plan* plan, rof_plan_info* info);
  *   col        [gather_entries]      int32  < num_nodes: feature row; >= num_nodes: partial row
  *   group_ptr  [num_groups+1]        int32  source range of each reuse group
  *   group_col  [group_sources]       int32
- *   items      [num_items][4]        int32  (begin, end, dst, 0); dst<0: segment slot -dst-1
+ *   items      [num_items][4]        int32  (begin, end, dst, mid); dst<0: segment slot -dst-1;
+ *                                            entries [begin,mid) are partial rows, [mid,end) feature rows
  *   split_rows [split_rows][4]       int32  (row, first_slot, slot_count, 0)
  * A plan built on a machine without a CUDA device can be exported but not run.
  */
 int rof_plan_export(const rof_plan* plan, int64_t* row_ptr, int32_t* col, int32_t* group_ptr,
                     int32_t* group_col, int32_t* items, int32_t* split_rows);
+
+/*
+ * Staged plans for the multi-GPU pipeline (no upstream counterpart: upstream is single-GPU).
+ * The feature matrix is owned in blocks of `block_rows` consecutive rows; block b becomes
+ * available in stage stage_of_block[b] (0 = already local, then the order in which peers'
+ * blocks arrive).  `whole` is split into `num_stages` plans over the same destination rows:
+ * stage k holds the entries whose source row arrives in stage k, and every reuse group is
+ * built in the stage in which its last source arrives.  Running the stages in order — stage 0
+ * plain, the others with ROF_PHASE_ACCUMULATE — gives the same sums as `whole`, while stage k
+ * only reads blocks that have arrived by then.  stages_out receives num_stages plans.
+ */
+int rof_plan_create_stages(const rof_plan* whole, int block_rows, const int32_t* stage_of_block,
+                           int num_blocks, int num_stages, rof_plan** stages_out, void* stream);
 
 /* Bytes of device scratch rof_aggregate() needs for feature width `dim`: the partial-sum
  * rows of phase A plus the segment sums of split rows.  256-byte aligned memory. */
@@ -152,7 +166,10 @@ int rof_aggregate(const rof_plan* plan, int mode, const float* x, int64_t ldx, i
  * stream with the same arguments; rof_aggregate() is ROF_PHASE_ALL.  Upstream's counterpart
  * of A and B are the two launches of ROF_v1 (reuse_conv_kernel.cu:665, 692).
  */
-enum rof_phase { ROF_PHASE_PARTIALS = 1, ROF_PHASE_GATHER = 2, ROF_PHASE_REDUCE = 4, ROF_PHASE_ALL = 7 };
+enum rof_phase {
+  ROF_PHASE_PARTIALS = 1, ROF_PHASE_GATHER = 2, ROF_PHASE_REDUCE = 4, ROF_PHASE_ALL = 7,
+  ROF_PHASE_ACCUMULATE = 8 /* modifier: out += result (stage >= 1 of a staged pass) instead of out = result */
+};
 
 int rof_aggregate_phases(const rof_plan* plan, int phases, int mode, const float* x, int64_t ldx,
                          int dim, const float* degrees, float* out, int64_t ldo, float* cache_result,

@@ -1,0 +1,111 @@
+"""The autograd function and layer (upstream reuse_conv.py:30-150) and the model stand-ins on the GPU."""
+import numpy as np
+import pytest
+import torch
+
+import rof_oracle
+from artifact_b200 import graphs, search
+from artifact_b200.models import ROF_GCN, ROF_GIN, ROF_inputInfo
+from artifact_b200.plan import AggregationPlan
+from artifact_b200.reuse_conv import ROF_GCNConv, ROF_GCNConvFunc
+from conftest import assert_close, load_golden
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def make_info(name):
+    g = load_golden(name)
+    info = ROF_inputInfo.from_layouts(g["indptr_dst"].astype(np.int64), g["layouts"], device=DEV)
+    return g, info
+
+
+@pytest.mark.parametrize("kernel_type", ["GNNA", "ROF_v1", "ROF_v2"])
+def test_layer_forward_backward_matches_oracle(kernel_type):
+    g, info = make_info("c1_full_ps2")          # symmetric graph with self-loops: backward is the true gradient
+    N, L, deg = g["N"], g["layouts"], g["degrees"]
+    torch.manual_seed(0)
+    layer = ROF_GCNConv(10, 6, add_self_loops=False, kernel_type=kernel_type, reuse_size=info.reuse_size).to(DEV)
+    assert layer.part_result_cache.shape == (info.reuse_size, 7) and layer.dimWorker == 6
+    x = torch.randn((N, 10), device=DEV, requires_grad=True)
+    y = layer(x, info)
+    w = torch.randn_like(y)
+    (y * w).sum().backward()
+    X, W = x.detach().cpu().numpy(), layer.weight.detach().cpu().numpy()
+    want = rof_oracle.GNNA_forward(X, W, L["original_column_index"], deg, L["part_pointers"], L["part2Node"],
+                                   exact64=True)[0] + layer.bias.detach().cpu().numpy()
+    assert_close(y.detach().cpu().numpy(), want, rel=2e-5, what="layer forward")
+    dX, dW = rof_oracle.GNNA_backward(w.cpu().numpy(), X, W, L["original_column_index"], deg, L["part_pointers"],
+                                      L["part2Node"], exact64=True)
+    assert_close(x.grad.cpu().numpy(), dX, rel=5e-5, abs_=1e-5, what="dX")
+    assert_close(layer.weight.grad.cpu().numpy(), dW, rel=5e-5, abs_=2e-4, what="dW")
+    assert_close(layer.bias.grad.cpu().numpy(), w.sum(0).cpu().numpy(), rel=1e-5, abs_=1e-4, what="db")
+
+
+def test_symmetric_backward_is_the_true_gradient():
+    """on a symmetric graph A_hat^T = A_hat, so autograd through a dense A_hat must agree"""
+    g, info = make_info("c1_full_ps3")
+    N, deg = g["N"], g["degrees"]
+    A = torch.zeros((N, N), dtype=torch.float64)
+    dst = np.repeat(np.arange(N), np.diff(g["indptr_dst"]))
+    A[dst, g["indices_src"]] = 1.0
+    s = torch.from_numpy(1.0 / np.sqrt(deg.astype(np.float64)))
+    A_hat = (s[:, None] * A * s[None, :]).to(DEV)
+    torch.manual_seed(1)
+    x = torch.randn((N, 8), device=DEV, requires_grad=True)
+    w = torch.randn((8, 5), device=DEV, requires_grad=True)
+    y = ROF_GCNConvFunc.apply(x, w, _with_cache(info, 5), False, "ROF_v2")
+    y.pow(2).sum().backward()
+    xd, wd = x.detach().double().requires_grad_(), w.detach().double().requires_grad_()
+    (A_hat @ (xd @ wd)).pow(2).sum().backward()
+    assert_close(x.grad.cpu().numpy(), xd.grad.cpu().numpy(), rel=1e-4, abs_=1e-4, what="dX vs dense autograd")
+    assert_close(w.grad.cpu().numpy(), wd.grad.cpu().numpy(), rel=1e-4, abs_=1e-3, what="dW vs dense autograd")
+
+
+def _with_cache(info, dim):
+    info.part_result_cache = torch.zeros((info.reuse_size, dim + 1), device=DEV)
+    info.dimWorker = min(dim, 32)
+    return info
+
+
+def test_argument_behaviour_like_upstream():
+    g, info = make_info("shared_prefix_12_ps3")
+    layer = ROF_GCNConv(4, 4, reuse_size=info.reuse_size).to(DEV)          # add_self_loops defaults to True ...
+    with pytest.raises(NotImplementedError):                                 # ... which raises, reuse_conv.py:72-73
+        layer(torch.ones((12, 4), device=DEV), info)
+    layer = ROF_GCNConv(4, 4, add_self_loops=False, kernel_type="nope", reuse_size=info.reuse_size).to(DEV)
+    with pytest.raises(NotImplementedError):
+        layer(torch.ones((12, 4), device=DEV), info)
+    with pytest.raises(NotImplementedError):
+        ROF_GCNConv(4, 4, weight_initializer="other")
+    assert ROF_GCNConv(4, 64, bias=False).dimWorker == 32 and ROF_GCNConv(4, 64, bias=False).bias is None
+
+
+def test_gcn_stack_trains_a_step_and_gin_runs():
+    g = graphs.config1()
+    L = search.search_graph(g, 3)
+    info = ROF_inputInfo.from_layouts(g.indptr_dst, L, device=DEV)
+    torch.manual_seed(0)
+    feats = (torch.rand((g.num_nodes, 1433), device=DEV) < 0.0127).float()
+    feats = feats / feats.sum(1, keepdim=True).clamp(min=1.0)
+    labels = torch.randint(0, 7, (g.num_nodes,), device=DEV)
+    for kt in ("GNNA", "ROF_v1", "ROF_v2"):
+        model = ROF_GCN(1433, 16, 7, 1, dropout=0.0, add_self_loops=False, reuse_size=info.reuse_size,
+                        kernel_type=kt).to(DEV)
+        opt = torch.optim.Adam(model.parameters(), lr=1e-2, weight_decay=5e-4)
+        losses = []
+        for _ in range(5):
+            opt.zero_grad()
+            loss = torch.nn.functional.cross_entropy(model(feats, info), labels)
+            loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        assert np.isfinite(losses).all() and losses[-1] < losses[0]
+    g3 = graphs.config3(0.02)
+    plan = AggregationPlan.from_parts(g3.num_nodes, torch.from_numpy(g3.indices_src).to(DEV),
+                                      torch.from_numpy(g3.indptr_dst.astype(np.int32)).to(DEV),
+                                      torch.arange(g3.num_nodes, dtype=torch.int32, device=DEV))
+    gin = ROF_GIN(128, 256, 40, 3).to(DEV)
+    with torch.no_grad():
+        out = gin(torch.randn((g3.num_nodes, 128), device=DEV), plan)
+    assert out.shape == (g3.num_nodes, 40) and torch.isfinite(out).all()

@@ -57,8 +57,9 @@ def test_items_cover_every_entry_once(golden, which):
     covered = np.zeros(len(ex["col"]), np.int32)
     seen_rows = set()
     lens = []
-    for b, e, dst, _ in ex["items"]:
+    for b, e, dst, mid in ex["items"]:
         covered[b:e] += 1
+        assert b <= mid <= e and (ex["col"][b:mid] >= N).all() and (ex["col"][mid:e] < N).all()
         lens.append(e - b)
         assert e - b <= plan.info["segment_edges"]
         if dst >= 0:

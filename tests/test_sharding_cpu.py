@@ -1,0 +1,84 @@
+"""The multi-GPU host logic with two gloo ranks on CPU: equal row blocks, per-block plans built
+from the same index tensors, and the all-gather of feature blocks.  The kernels cannot run
+here, so each rank evaluates its exported plan with numpy; the concatenated blocks must equal
+the oracle on the whole graph."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from conftest import ROOT, layout_args, load_golden
+
+
+def eval_plan_numpy(ex, x, n):
+    """out[r] = sum over the row's entries; entries >= n are partial rows of the exported groups"""
+    part = np.stack([x[ex["group_col"][ex["group_ptr"][g]:ex["group_ptr"][g + 1]]].astype(np.float64).sum(0)
+                     for g in range(len(ex["group_ptr"]) - 1)]) if len(ex["group_ptr"]) > 1 else np.zeros((0, x.shape[1]))
+    out = np.zeros((len(ex["row_ptr"]) - 1, x.shape[1]))
+    for r in range(out.shape[0]):
+        for c in ex["col"][ex["row_ptr"][r]:ex["row_ptr"][r + 1]]:
+            out[r] += x[c] if c < n else part[c - n]
+    return out
+
+
+def _worker(rank, world, port, name, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from artifact_b200.plan import AggregationPlan
+    from artifact_b200.sharding import ShardedFeatures
+    g = load_golden(name)
+    n, dim = g["N"], 6
+    x = np.random.default_rng(4).standard_normal((n, dim)).astype(np.float32)
+    feats = ShardedFeatures(n, dim, rank, world, torch.device("cpu"))
+    r0, r1 = feats.blocks[rank]
+    local = torch.zeros((feats.block, dim))
+    local[:r1 - r0] = torch.from_numpy(x[r0:r1])
+    x_full = feats.all_gather(local).numpy()
+    assert np.array_equal(x_full, x)                                  # every rank now holds all rows
+    plan = AggregationPlan.from_v2(n, *layout_args(g["layouts"], "v2"), rows=(r0, r1))
+    out = eval_plan_numpy(plan.export(), x_full, n)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (r0, r1, out))
+    if rank == 0:
+        q.put(np.concatenate([o for _, _, o in sorted(gathered, key=lambda t: t[0])]))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name", ["c5_n1024_ps2", "shared_prefix_12_ps3"])
+@pytest.mark.parametrize("world", [2, 3])
+def test_two_rank_row_blocks_equal_whole_graph(name, world):
+    import rof_oracle
+    g = load_golden(name)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + world * 7 + len(name)) % 2000
+    procs = [ctx.Process(target=_worker, args=(r, world, port, name, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    x = np.random.default_rng(4).standard_normal((g["N"], 6)).astype(np.float32)
+    L = g["layouts"]
+    want = rof_oracle.aggregate_v2(x, L["uniqpart_column_index"], g["degrees"], L["uniqpart_pointers"],
+                                   L["part2Node_ptr"], L["part2Node_col"], "sum", exact64=True)
+    assert np.allclose(got, want, rtol=1e-6, atol=1e-6)
+
+
+def test_row_blocks_cover_and_pad():
+    from artifact_b200.sharding import row_blocks
+    for n in (0, 1, 7, 8, 1000):
+        for w in (1, 2, 3, 8):
+            blk, blocks = row_blocks(n, w)
+            assert blk * w >= n and len(blocks) == w
+            assert blocks[0][0] == 0 and blocks[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
+            assert all(0 <= r1 - r0 <= blk for r0, r1 in blocks)
