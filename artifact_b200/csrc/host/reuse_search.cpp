@@ -24,6 +24,7 @@
 #include <cstdint>
 #include <cstring>
 #include <numeric>
+#include <parallel/algorithm>
 #include <vector>
 #include <omp.h>
 
@@ -221,10 +222,56 @@ rofh_search* rofh_reuse_search(int n, const int64_t* indptr_dst, const int32_t* 
   build_bitmaps(outg, bitmap_budget_bytes, bm);
   std::vector<int32_t>& nums = S->arr[ROFH_INTERSECTION_NUM];
   nums.assign((size_t)P, 0);
-#pragma omp parallel for schedule(dynamic, 2048)
-  for (int64_t p = 0; p < P; ++p) {
-    if (part_ptr[(size_t)p + 1] - part_ptr[(size_t)p] != ps) continue;
-    nums[(size_t)p] = (int32_t)intersect_part(outg, bm, indices_src + part_ptr[(size_t)p], ps, nullptr);
+  {
+    // Many parts hold the same source tuple (hub pairs recur in thousands of rows) and the
+    // expensive ones are exactly those: count each distinct tuple once.  Parts are grouped
+    // by sorting (hash of tuple, part id); equal hashes are confirmed by comparing tuples.
+    struct Key { uint64_t h; u32 p; bool operator<(const Key& o) const { return h < o.h || (h == o.h && p < o.p); } };
+    std::vector<Key> keys;
+    keys.reserve((size_t)P);
+    for (int64_t p = 0; p < P; ++p)
+      if (part_ptr[(size_t)p + 1] - part_ptr[(size_t)p] == ps) keys.push_back(Key{0, (u32)p});
+    const int64_t F = (int64_t)keys.size();
+#pragma omp parallel for schedule(static, 4096)
+    for (int64_t i = 0; i < F; ++i) {
+      const int32_t* t = indices_src + part_ptr[keys[(size_t)i].p];
+      uint64_t h = 0x9E3779B97F4A7C15ull;
+      for (int k = 0; k < ps; ++k) {
+        h ^= (uint64_t)(u32)t[k] + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
+        h *= 0xBF58476D1CE4E5B9ull;
+      }
+      keys[(size_t)i].h = h;
+    }
+    __gnu_parallel::sort(keys.begin(), keys.end());
+    auto same_tuple = [&](u32 a, u32 b) {
+      return std::memcmp(indices_src + part_ptr[a], indices_src + part_ptr[b], sizeof(int32_t) * (size_t)ps) == 0;
+    };
+    // run starts: a new run begins where the hash changes; inside a run of equal hashes
+    // (almost always one tuple) every part is compared with the run's representatives
+    std::vector<int64_t> run_start;
+    for (int64_t i = 0; i < F; ++i)
+      if (i == 0 || keys[(size_t)i].h != keys[(size_t)i - 1].h) run_start.push_back(i);
+    run_start.push_back(F);
+    const int64_t R = (int64_t)run_start.size() - 1;
+#pragma omp parallel
+    {
+      std::vector<std::pair<u32, int32_t>> reps;  // (representative part, its count) within one run
+#pragma omp for schedule(dynamic, 512)
+      for (int64_t r = 0; r < R; ++r) {
+        reps.clear();
+        for (int64_t i = run_start[(size_t)r]; i < run_start[(size_t)r + 1]; ++i) {
+          const u32 p = keys[(size_t)i].p;
+          int32_t cnt = -1;
+          for (auto& rp : reps)
+            if (same_tuple(rp.first, p)) { cnt = rp.second; break; }
+          if (cnt < 0) {
+            cnt = (int32_t)intersect_part(outg, bm, indices_src + part_ptr[p], ps, nullptr);
+            reps.emplace_back(p, cnt);
+          }
+          nums[p] = cnt;
+        }
+      }
+    }
   }
   S->seconds[1] = omp_get_wtime() - t0; t0 = omp_get_wtime();
 

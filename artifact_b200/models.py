@@ -93,11 +93,11 @@ class SumAggregate(torch.autograd.Function):
     @staticmethod
     def forward(ctx, h, plan, plan_t, degrees, mode):
         ctx.plan_t, ctx.degrees, ctx.mode = (plan_t or plan), degrees, mode
-        return plan.aggregate(h.contiguous(), degrees, mode)
+        return plan.aggregate(h.contiguous(), degrees, mode, tiles="auto")
 
     @staticmethod
     def backward(ctx, g):
-        return ctx.plan_t.aggregate(g.contiguous(), ctx.degrees, ctx.mode), None, None, None, None
+        return ctx.plan_t.aggregate(g.contiguous(), ctx.degrees, ctx.mode, tiles="auto"), None, None, None, None
 
 
 class ROF_GIN(torch.nn.Module):

@@ -97,7 +97,7 @@ def SAG(input, row_pointers, column_index, degrees, part_pointers, part2Node, pa
                  (degrees, "degrees"), (part_pointers, "part_pointers"), (part2Node, "part2Node")):
         _check_input(t, n)
     plan = plan_for_parts(input.size(0), column_index, part_pointers, part2Node)
-    return plan.aggregate(input, None, "sum")
+    return plan.aggregate(input, None, "sum", tiles="auto")
 
 
 # ---- reuse_conv.cpp:158-205 ---------------------------------------------------------------
@@ -107,7 +107,7 @@ def GNNA_forward(input, weight, column_index, degrees, part_pointers, part2Node,
         _check_input(t, n)
     plan = plan_for_parts(input.size(0), column_index, part_pointers, part2Node)
     tmp = torch.mm(input, weight)                                   # reuse_conv_kernel.cu:302
-    return [plan.aggregate(tmp, degrees, "gcn")]
+    return [plan.aggregate(tmp, degrees, "gcn", tiles="auto")]
 
 
 def GNNA_backward(d_output, X, weight, column_index, degrees, part_pointers, part2Node, partSize, dimWorker,
@@ -116,7 +116,7 @@ def GNNA_backward(d_output, X, weight, column_index, degrees, part_pointers, par
                  (degrees, "degrees"), (part_pointers, "part_pointers"), (part2Node, "part2Node")):
         _check_input(t, n)
     plan = plan_for_parts(d_output.size(0), column_index, part_pointers, part2Node)
-    return _backward_tail(plan.aggregate(d_output, degrees, "gcn"), X, weight)
+    return _backward_tail(plan.aggregate(d_output, degrees, "gcn", tiles="auto"), X, weight)
 
 
 # ---- reuse_conv.cpp:208-285 ---------------------------------------------------------------
@@ -155,7 +155,7 @@ def reuse_forward_v2(input, weight, uniqpart_column_index, degrees, uniqpart_poi
         _check_input(t, n)
     plan = plan_for_v2(input.size(0), uniqpart_column_index, uniqpart_pointers, part2Node_ptr, part2Node_col)
     tmp = torch.mm(input, weight)                                   # reuse_conv_kernel.cu:971
-    return [plan.aggregate(tmp, degrees, "gcn")]
+    return [plan.aggregate(tmp, degrees, "gcn", tiles="auto")]
 
 
 def reuse_backward_v2(d_output, X, W, uniqpart_column_index, degrees, uniqpart_pointers, part2Node_ptr, part2Node_col,
@@ -165,4 +165,4 @@ def reuse_backward_v2(d_output, X, W, uniqpart_column_index, degrees, uniqpart_p
                  (part2Node_col, "part2Node_col")):
         _check_input(t, n)
     plan = plan_for_v2(d_output.size(0), uniqpart_column_index, uniqpart_pointers, part2Node_ptr, part2Node_col)
-    return _backward_tail(plan.aggregate(d_output, degrees, "gcn"), X, W)
+    return _backward_tail(plan.aggregate(d_output, degrees, "gcn", tiles="auto"), X, W)

@@ -226,7 +226,7 @@ def prepare_workload(args, rank, world):
 def workload_config(args, g, ratios):
     c = {"workload": f"{args.workload}: seeded synthetic graph N={g.num_nodes} E={g.num_edges}, fp32 features "
                      f"D={args.dim}, {args.mode} aggregation, forward+backward pass per step",
-         "part_size": args.part_size, "layout": "ROF_v2", "scale": args.scale,
+         "part_size": args.part_size, "layout": "ROF_v2", "scale": args.scale, "source_tiles": args.tiles,
          "l2": "feature matrix and index arrays together exceed L2 (126 MB); no flush between iterations",
          "parallelism": (f"row-block x{args.gpus}, " + ("all-gather rounds overlapped with staged aggregation"
                                                         if args.pipeline else "all-gather then aggregate"))
@@ -250,6 +250,7 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (tests / profiling only)")
     ap.add_argument("--no-pipeline", dest="pipeline", action="store_false",
                     help="N > 1: one all-gather, then the aggregation (no overlap)")
+    ap.add_argument("--tiles", default="auto", help="source tiles per pass on one GPU: auto or an integer")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--only-kernel", action="store_true", help="skip sweep, CPU baseline and e2e (profiling)")
@@ -314,6 +315,7 @@ def main():
     ev = lambda: torch.cuda.Event(enable_timing=True)
     gather_events = []
     launches = [0]
+    tiles = (plan.auto_tiles(D) if args.tiles == "auto" else int(args.tiles)) if world == 1 else 1
     pipes = {}
     if world > 1 and args.pipeline:
         px = PipelinedAggregator(plan, feat_x)
@@ -326,16 +328,8 @@ def main():
             launches[0] += pipe.launches
             return
         xs = feat.all_gather(src_loc) if world > 1 else feat.full[:n]
-        if timed_gather:
-            p.aggregate(xs, deg, mode, out=out, phases=1); launches[0] += p.last_launch_count()
-            e0, e1 = ev(), ev()
-            e0.record()
-            p.aggregate(xs, deg, mode, out=out, phases=2); launches[0] += p.last_launch_count()
-            e1.record()
-            p.aggregate(xs, deg, mode, out=out, phases=4); launches[0] += p.last_launch_count()
-            gather_events.append((e0, e1))
-        else:
-            p.aggregate(xs, deg, mode, out=out); launches[0] += p.last_launch_count()
+        p.aggregate(xs, deg, mode, out=out, tiles=tiles, gather_events=gather_events if timed_gather else None)
+        launches[0] += p.last_launch_count()
 
     def step(p, timed_gather=False):
         one_pass(p, x_loc, feat_x, out_f, timed_gather)
@@ -383,7 +377,9 @@ def main():
             if i >= 3:
                 gather_events.append((e0, e1))
         torch.cuda.synchronize()
-    gms = float(np.mean([a.elapsed_time(b) for a, b in gather_events]))
+    # one pass = `tiles` phase-B launches (one per source tile); report the pass as one unit
+    per_pass = max(tiles, 1) if not pipes else 1
+    gms = float(np.sum([a.elapsed_time(b) for a, b in gather_events])) / (len(gather_events) / per_pass)
     info = plan.info
     row_b = 4.0 * D
     gather_bytes = row_b * (info["gather_entries"] + (r1 - r0)) + 4.0 * info["gather_entries"] + 4.0 * (r1 - r0 + 1)
@@ -392,6 +388,7 @@ def main():
     achieved = gather_bytes / (gms / 1e3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "traffic": None, "kernel": "gather_rows_kernel (phase B)", "ms_per_launch": gms,
+                "launches_per_pass": per_pass,
                 "algorithmic_bytes_per_launch": gather_bytes, "peak_kind": f"{peak_kind} copy bandwidth",
                 "note": "algorithmic bytes = (gathered rows + written rows) x 4D + 4 per index; hub rows are "
                         "re-read from L2, so achieved can exceed the DRAM peak; see profiles/ for DRAM traffic"}
@@ -454,12 +451,14 @@ def main():
             for m in ("sum", "mean"):
                 row = {"D": d, "mode": m}
                 for nm, p in (("reuse", plan), ("plain", plain)):
+                    t = p.auto_tiles(d)
+                    row[nm + "_tiles"] = t
                     for _ in range(3):
-                        p.aggregate(xs, deg, m, out=o)
+                        p.aggregate(xs, deg, m, out=o, tiles=t)
                     s, e = ev(), ev()
                     s.record()
                     for _ in range(5):
-                        p.aggregate(xs, deg, m, out=o)
+                        p.aggregate(xs, deg, m, out=o, tiles=t)
                     e.record(); torch.cuda.synchronize()
                     ms = s.elapsed_time(e) / 5
                     row[nm] = {"ms": round(ms, 4), "gedges_per_s": round(E / ms / 1e6, 3),

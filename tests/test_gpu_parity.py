@@ -244,3 +244,22 @@ def test_current_stream_is_honoured():
         out = plan.aggregate(y, None, "sum")
     s.synchronize()
     assert torch.allclose(out, ref * 2.0, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("tiles", [2, 3, 8])
+@pytest.mark.parametrize("mode", ["sum", "gcn", "mean"])
+def test_source_tiles_give_the_same_sums(tiles, mode):
+    """walking the feature matrix in source tiles (per-tile plans accumulated into out) only
+    reorders the adds"""
+    g = load_golden("c2_n640_ps2")
+    N = g["N"]
+    x = np.random.default_rng(12).standard_normal((N, 40)).astype(np.float32)
+    deg = torch.from_numpy(np.maximum(g["degrees"], 1.0)).to(DEV)
+    plan = AggregationPlan.from_v2(N, *[dev_i32(a) for a in layout_args(g["layouts"], "v2")])
+    events = []
+    got = plan.aggregate(torch.from_numpy(x).to(DEV), deg, mode, tiles=tiles, gather_events=events).cpu().numpy()
+    assert len(events) == tiles and plan.last_launch_count() >= tiles
+    gg = dict(g)
+    gg["degrees"] = np.maximum(g["degrees"], 1.0)
+    assert_close(got, oracle(gg, "v2", x, mode), what=f"{tiles} tiles {mode}")
+    assert plan.auto_tiles(40) == 1 and plan.auto_tiles(1 << 20) >= 1
