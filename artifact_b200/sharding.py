@@ -61,24 +61,42 @@ class ShardedAggregator:
         return self.plan.aggregate(x_full, degrees, mode, out=out, phases=phases)
 
 
+def stage_schedule(world, growth=3):
+    """Which peers' blocks travel in which stage: stage 0 is the rank's own block, each later
+    stage fetches `growth` times as many peer blocks as the one before (1, 3, 9, ...), so the
+    aggregation of one stage covers the transfer of the next as long as moving a block takes no
+    longer than `growth` times aggregating one, and the number of stages (kernel launches and
+    NCCL calls per pass) grows with log(world), not world.  Returns a list of lists of ring
+    offsets k (the block of rank (r + k) % world): [[0], [1], [2, 3, 4], [5, 6, 7]] for 8 ranks."""
+    stages, k, size = [[0]], 1, 1
+    while k < world:
+        stages.append(list(range(k, min(world, k + size))))
+        k += size
+        size *= growth
+    return stages
+
+
 class PipelinedAggregator:
     """All-gather overlapped with aggregation, stage by stage.
 
-    Rank r reads its own block in stage 0 and the block of rank (r + k) % world in stage k.
-    The blocks travel as world-1 rounds of paired send/receive on a side stream (round k: send
-    the own block to rank r-k, receive the block of rank r+k; NVSwitch gives every pair full
-    bandwidth), and the per-stage plans (AggregationPlan.stages) run on the compute stream as
-    soon as their round has landed, adding into `out`.  The result equals the whole-plan
-    aggregate up to the order of the fp32 adds.
+    Rank r reads its own block in stage 0 and the blocks of ranks (r + k) % world, k in the
+    stage's offsets (see stage_schedule), in the later stages.  Each stage's blocks travel as one
+    group of paired sends/receives on a side stream (send the own block to rank r-k, receive the
+    block of rank r+k; NVSwitch gives every pair full bandwidth), and the per-stage plans
+    (AggregationPlan.stages) run on the compute stream as soon as their blocks have landed,
+    adding into `out`.  The result equals the whole-plan aggregate up to the order of the fp32
+    adds.  Every kernel reads this GPU's memory only.
     """
 
-    def __init__(self, plan, features: ShardedFeatures, stage_plans=None):
+    def __init__(self, plan, features: ShardedFeatures, stage_plans=None, schedule=None):
         f = features
         r0, r1 = f.blocks[f.rank]
         if (plan.info["row_begin"], plan.info["row_end"]) != (r0, r1):
             raise RuntimeError("the plan does not cover this rank's row block")
         self.features, self.whole = f, plan
-        stage_of_block = [(b - f.rank) % f.world for b in range(f.world)]
+        self.schedule = schedule or stage_schedule(f.world)
+        stage_of_offset = {k: s for s, ks in enumerate(self.schedule) for k in ks}
+        stage_of_block = [stage_of_offset[(b - f.rank) % f.world] for b in range(f.world)]
         if stage_plans is not None:
             self.stage_plans = stage_plans
         else:
@@ -86,7 +104,7 @@ class PipelinedAggregator:
         dev = f.full.device
         self.comm_stream = torch.cuda.Stream(dev) if f.world > 1 else None
         self.ready = torch.cuda.Event() if f.world > 1 else None
-        self.landed = [torch.cuda.Event() for _ in range(f.world)]
+        self.landed = [torch.cuda.Event() for _ in self.schedule]
         self.launches = 0
 
     def aggregate(self, x_local, degrees, mode, out):
@@ -100,17 +118,19 @@ class PipelinedAggregator:
             self.ready.record(cur)
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_event(self.ready)
-                for k in range(1, R):
-                    src = (r + k) % R
-                    ops = [dist.P2POp(dist.isend, f.local_view(), (r - k) % R, group=f.group),
-                           dist.P2POp(dist.irecv, f.full[src * blk:(src + 1) * blk], src, group=f.group)]
+                for s in range(1, len(self.schedule)):
+                    ops = []
+                    for k in self.schedule[s]:
+                        src = (r + k) % R
+                        ops.append(dist.P2POp(dist.isend, f.local_view(), (r - k) % R, group=f.group))
+                        ops.append(dist.P2POp(dist.irecv, f.full[src * blk:(src + 1) * blk], src, group=f.group))
                     for w in dist.batch_isend_irecv(ops):
                         w.wait()
-                    self.landed[k].record(self.comm_stream)
+                    self.landed[s].record(self.comm_stream)
         self.launches = 0
-        for k, p in enumerate(self.stage_plans):
-            if k:
-                cur.wait_event(self.landed[k])
-            p.aggregate(x_full, degrees, mode, out=out, accumulate=k > 0)
+        for s, p in enumerate(self.stage_plans):
+            if s:
+                cur.wait_event(self.landed[s])
+            p.aggregate(x_full, degrees, mode, out=out, accumulate=s > 0)
             self.launches += p.last_launch_count()
         return out

@@ -308,8 +308,9 @@ def main():
     feat_x = ShardedFeatures(n, D, rank, world, dev)
     feat_g = ShardedFeatures(n, D, rank, world, dev)
     feat_x.full.normal_(generator=gen); feat_g.full.normal_(generator=gen)
-    x_loc = feat_x.local_view().clone()
-    g_loc = feat_g.local_view().clone()
+    # this rank's block of features / gradients lives inside the full buffers (in-place all-gather)
+    x_loc = feat_x.local_view()
+    g_loc = feat_g.local_view()
     out_f = torch.empty((r1 - r0, D), device=dev)
     out_b = torch.empty((r1 - r0, D), device=dev)
     ev = lambda: torch.cuda.Event(enable_timing=True)
@@ -324,10 +325,10 @@ def main():
     def one_pass(p, src_loc, feat, out, timed_gather=False):
         if pipes and p is plan:       # all-gather rounds overlapped with the per-stage aggregation
             pipe = pipes[id(feat)]
-            pipe.aggregate(src_loc, deg, mode, out)
+            pipe.aggregate(None, deg, mode, out)
             launches[0] += pipe.launches
             return
-        xs = feat.all_gather(src_loc) if world > 1 else feat.full[:n]
+        xs = feat.all_gather(None) if world > 1 else feat.full[:n]
         p.aggregate(xs, deg, mode, out=out, tiles=tiles, gather_events=gather_events if timed_gather else None)
         launches[0] += p.last_launch_count()
 
@@ -410,13 +411,31 @@ def main():
         h_of = torch.empty((r1 - r0, D), pin_memory=True)
         h_ob = torch.empty((r1 - r0, D), pin_memory=True)
 
+        # the caller's own streams around the API: uploads on one copy stream (the gradient's upload
+        # overlaps the forward pass), downloads on another (the forward result's download overlaps
+        # the backward pass); the aggregation itself runs on the current stream
+        cur = torch.cuda.current_stream(dev)
+        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+        up_x, up_g, done_f, done_b, down = (torch.cuda.Event() for _ in range(5))
+        done_f.record(cur); done_b.record(cur)
+
         def e2e_step():
-            x_loc.copy_(h_x, non_blocking=True)
-            one_pass(plan, x_loc, feat_x, out_f)
-            h_of.copy_(out_f, non_blocking=True)
-            g_loc.copy_(h_g, non_blocking=True)
-            one_pass(plan, g_loc, feat_g, out_b)
-            h_ob.copy_(out_b, non_blocking=True)
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(done_f)                    # previous forward pass has read x
+                x_loc.copy_(h_x, non_blocking=True); up_x.record(s_in)
+                s_in.wait_event(done_b)
+                g_loc.copy_(h_g, non_blocking=True); up_g.record(s_in)
+            cur.wait_event(up_x)
+            one_pass(plan, x_loc, feat_x, out_f); done_f.record(cur)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done_f)
+                h_of.copy_(out_f, non_blocking=True)
+            cur.wait_event(up_g)
+            one_pass(plan, g_loc, feat_g, out_b); done_b.record(cur)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done_b)
+                h_ob.copy_(out_b, non_blocking=True); down.record(s_out)
+            cur.wait_event(down)                           # the step ends when both results are on the host
 
         e2e_steps = max(3, min(args.steps, 10))
         for _ in range(3):

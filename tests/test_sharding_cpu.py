@@ -82,3 +82,13 @@ def test_row_blocks_cover_and_pad():
             assert blocks[0][0] == 0 and blocks[-1][1] == n
             assert all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
             assert all(0 <= r1 - r0 <= blk for r0, r1 in blocks)
+
+
+def test_stage_schedule_covers_every_peer_once():
+    from artifact_b200.sharding import stage_schedule
+    for w in (1, 2, 3, 4, 5, 8, 16):
+        sch = stage_schedule(w)
+        assert sch[0] == [0]
+        flat = [k for s in sch for k in s]
+        assert flat == list(range(w))
+        assert len(sch) <= 2 + int(np.ceil(np.log(max(w, 1)) / np.log(3))) + 1
