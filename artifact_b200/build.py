@@ -19,7 +19,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "_lib")
 INCLUDE = os.path.join(ROOT, "include")
 
-CUDA_SOURCES = ["plan.cu", "kernels.cu", "api.cu", "stages.cu"]
+CUDA_SOURCES = ["plan.cu", "kernels.cu", "api.cu", "stages.cu", "static_scratch.cu"]
 HOST_SOURCES = [os.path.join("host", "graphgen.cpp"), os.path.join("host", "reuse_search.cpp")]
 
 NVCC_FLAGS = [

@@ -269,6 +269,33 @@ class AggregationPlan:
                     gather_events.append((e0, e1))
         return out
 
+    def aggregate_static_scratch(self, x, degrees=None, mode="gcn", out=None):
+        """rof_aggregate_static_scratch(): the same pass with the library's built-in 32 MiB scratch
+        instead of a workspace, for callers that cannot allocate device memory at call time.  Here
+        torch still allocates `out` when none is given — pass `out` to allocate nothing at all.
+        Raises RofError (ROF_ERR_WORKSPACE) when the pass needs more scratch than is built in."""
+        i = self.info
+        if not x.is_cuda or x.dtype != torch.float32 or x.dim() != 2 or (x.stride(1) != 1 and x.size(1) > 1):
+            raise RuntimeError("x must be a 2-D float32 CUDA tensor with unit column stride")
+        if x.size(0) != i["num_nodes"]:
+            raise RuntimeError(f"x has {x.size(0)} rows, the plan was built for {i['num_nodes']} nodes")
+        dim, rows = x.size(1), i["row_end"] - i["row_begin"]
+        if out is None:
+            out = torch.empty((rows, dim), dtype=torch.float32, device=x.device)
+        elif tuple(out.shape) != (rows, dim) or out.dtype != torch.float32 or not out.is_cuda:
+            raise RuntimeError("out must be a float32 CUDA tensor of shape [rows, dim]")
+        deg_ptr = None
+        if MODES[mode] != MODES["sum"]:
+            if degrees is None or not degrees.is_cuda or degrees.dtype != torch.float32 or degrees.numel() != i["num_nodes"]:
+                raise RuntimeError("degrees must be a float32 CUDA tensor with one entry per node")
+            deg_ptr = ctypes.c_void_p(degrees.data_ptr())
+        with _device_guard(x.device):
+            _native.check(_native.cuda().rof_aggregate_static_scratch(
+                self._h, MODES[mode], ctypes.c_void_p(x.data_ptr()), x.stride(0) if x.size(0) > 1 else dim, dim,
+                deg_ptr, ctypes.c_void_p(out.data_ptr()), out.stride(0) if rows > 1 else dim,
+                ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)))
+        return out
+
     def last_launch_count(self):
         return self.launches
 

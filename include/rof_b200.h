@@ -175,6 +175,25 @@ int rof_aggregate_phases(const rof_plan* plan, int phases, int mode, const float
                          int dim, const float* degrees, float* out, int64_t ldo, float* cache_result,
                          void* workspace, int64_t workspace_bytes, void* stream);
 
+/*
+ * The same pass for callers that cannot allocate device memory (no counterpart in upstream,
+ * whose wrappers allocate freely with torch): no workspace argument — the scratch is a fixed
+ * array of ROF_STATIC_SCRATCH_BYTES inside the library, reserved on every GPU that loads it
+ * until the process exits.  Meant for hosts that gave all of HBM to their own pool at start-up,
+ * or that call from a section where a device allocation (a device-wide synchronisation) is not
+ * acceptable.  Allocates nothing; no cache_result mirror.
+ *   - A pass whose rof_plan_workspace_bytes(plan, dim) exceeds ROF_STATIC_SCRATCH_BYTES returns
+ *     ROF_ERR_WORKSPACE and launches nothing.
+ *   - The first call on each device looks up the array's device address; make that call during
+ *     start-up, with the device current, before any stream capture begins.
+ *   - All calls on a GPU share the array, which keeps the previous call's contents (each pass
+ *     writes every scratch row before reading it, so nothing has to be cleared).  Calls that
+ *     overlap on the GPU race on it: keep them ordered on one stream.
+ */
+#define ROF_STATIC_SCRATCH_BYTES (32u << 20)
+int rof_aggregate_static_scratch(const rof_plan* plan, int mode, const float* x, int64_t ldx, int dim,
+                                 const float* degrees, float* out, int64_t ldo, void* stream);
+
 /* Number of kernel launches the last rof_aggregate() on this thread enqueued. */
 int rof_last_launch_count(void);
 
