@@ -5,10 +5,11 @@
 // atomics (reuse_conv_kernel.cu:230-285, 521-600, 879-953).  Here the same index tensors are
 // transposed once, on the host, into rows of entries: an entry < N names a feature row, an
 // entry >= N names the partial sum of reuse group (entry - N).  Rows longer than
-// kSegmentEdges are cut into segments whose sums are combined by a second small kernel in a
+// the segment length are cut into segments whose sums are combined by a second small kernel in a
 // fixed order, so the result is deterministic.  Work items are ordered longest first so the
 // hardware block scheduler balances the power-law tail.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <numeric>
@@ -137,19 +138,27 @@ int finalize_plan(HostPlan& hp, rof_plan** out, cudaStream_t stream) {
 
   std::vector<WorkItem> items;
   std::vector<SplitRow> split;
-  items.reserve((size_t)rows + (size_t)(entries / kSegmentEdges) + 1);
+  // Segment length: at most kMaxSegmentEdges, shorter when the plan is small, so that there are
+  // always many more work items than resident warps (148 SMs x 32 warps): with 1024-entry
+  // segments a 14.5M-entry plan (one eighth of the 114.6M-edge graph) ran as two waves of
+  // segments and lost 25 % to the tail.
+  int seg = kMaxSegmentEdges;
+  while (seg > kMinSegmentEdges && entries / seg < kTargetSegments) seg /= 2;
+  if (const char* env = std::getenv("ROF_SEGMENT_EDGES")) seg = std::max(32, std::atoi(env));
+  p->segment_edges = seg;
+  items.reserve((size_t)rows + (size_t)(entries / seg) + 1);
   int slots = 0;
   for (int32_t r : order) {
     const int64_t b = hp.row_ptr[r], en = hp.row_ptr[r + 1];
     const int64_t len = en - b;
-    if (len <= kSegmentEdges) {
+    if (len <= seg) {
       items.push_back(WorkItem{(int32_t)b, (int32_t)en, hp.row_begin + r, (int32_t)row_mid[(size_t)r]});
     } else {
-      const int nseg = (int)((len + kSegmentEdges - 1) / kSegmentEdges);
+      const int nseg = (int)((len + seg - 1) / seg);
       split.push_back(SplitRow{hp.row_begin + r, slots, nseg, 0});
       for (int s = 0; s < nseg; ++s) {
-        const int64_t sb = b + (int64_t)s * kSegmentEdges;
-        const int64_t se = std::min(en, sb + kSegmentEdges);
+        const int64_t sb = b + (int64_t)s * seg;
+        const int64_t se = std::min(en, sb + seg);
         const int64_t sm = std::min(se, std::max(sb, row_mid[(size_t)r]));
         items.push_back(WorkItem{(int32_t)sb, (int32_t)se, -(slots + s) - 1, (int32_t)sm});
       }
@@ -453,7 +462,7 @@ int rof_plan_get_info(const rof_plan* p, rof_plan_info* info) {
   info->num_items = p->num_items;
   info->split_rows = p->num_split_rows;
   info->num_slots = p->num_slots;
-  info->segment_edges = kSegmentEdges;
+  info->segment_edges = p->segment_edges;
   return ROF_OK;
 }
 

@@ -28,7 +28,9 @@ struct __align__(16) SplitRow {
   int32_t pad;
 };
 
-constexpr int kSegmentEdges = 1024;  // longest run of entries one work item sums
+constexpr int kMaxSegmentEdges = 1024;   // longest run of entries one work item sums
+constexpr int kMinSegmentEdges = 128;
+constexpr int64_t kTargetSegments = 75000;  // ~16 work items per resident warp of a B200
 
 }  // namespace rof
 
@@ -44,6 +46,7 @@ struct rof_plan {
   int num_items = 0;      // phase B
   int num_split_rows = 0;
   int num_slots = 0;
+  int segment_edges = 0;  // rows longer than this are split
 
   // device arrays
   int32_t* d_col = nullptr;           // [gather_entries + group_sources]: phase-B entries, then group sources

@@ -29,6 +29,7 @@ class ROF_inputInfo:
         self.part2Node_ptr, self.part2Node_col = part2Node_ptr, part2Node_col
         self.dimWorker = 32
         self.part_result_cache = None
+        self.transposed = None      # optional ROF_inputInfo of the transposed graph (exact backward, directed graphs)
 
     @classmethod
     def from_layouts(cls, indptr_dst, layouts, warpPerBlock=4, device=None):
@@ -47,7 +48,16 @@ class ROF_inputInfo:
     def reuse_size(self):
         return int(self.part_pointers_cache.shape[0]) - 1
 
+    def with_transposed(self, other):
+        """attach the layouts of the transposed graph; `other.degrees` is replaced by this graph's
+        in-degrees, because A_hat^T = D^-1/2 A^T D^-1/2 keeps the forward normalisation"""
+        other.degrees = self.degrees
+        self.transposed = other
+        return self
+
     def to(self, device):
+        if self.transposed is not None:
+            self.transposed.to(device)
         for f in _TENSOR_FIELDS:
             v = getattr(self, f)
             if isinstance(v, torch.Tensor):

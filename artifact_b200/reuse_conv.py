@@ -52,7 +52,11 @@ class ROF_GCNConvFunc(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_output):
         x, weight = ctx.saved_tensors
-        info = ctx.info
+        # upstream aggregates grad_output with the forward operator, which is the true gradient
+        # only for a symmetric graph (ROF_main.py:62).  When the caller attached the layouts of
+        # the transposed graph as `inputInfo.transposed` (same `degrees`), they are used instead
+        # and the gradient is exact for directed graphs too.
+        info = getattr(ctx.info, "transposed", None) or ctx.info
         ps, dw, wpb = ctx.launch
         grad_output = grad_output.contiguous()
         if ctx.kernel_type == "GNNA":
@@ -61,13 +65,20 @@ class ROF_GCNConvFunc(torch.autograd.Function):
         elif ctx.kernel_type == "ROF_v1":
             d_input, d_weight = ROF.reuse_backward_v1(grad_output, x, weight, info.column_index, info.degrees,
                                                       info.part_pointers, info.part2Node, ps, dw, wpb,
-                                                      ctx.cache, info.part_cache_flagindex,
+                                                      ctx.cache if info is ctx.info else _scratch_cache(info, grad_output), info.part_cache_flagindex,
                                                       info.part_pointers_cache, info.column_index_cache)
         else:
             d_input, d_weight = ROF.reuse_backward_v2(grad_output, x, weight, info.uniqpart_column_index,
                                                       info.degrees, info.uniqpart_pointers, info.part2Node_ptr,
                                                       info.part2Node_col, ps, dw, wpb)
         return d_input, d_weight, None, None, None
+
+
+def _scratch_cache(info, grad_output):
+    """a [groups, dim+1] buffer for the ROF_v1 backward over the transposed layouts (its group count
+    differs from the forward's, so the layer's own part_result_cache does not fit)"""
+    groups = int(info.part_pointers_cache.shape[0]) - 1
+    return torch.empty((groups, grad_output.size(1) + 1), dtype=grad_output.dtype, device=grad_output.device)
 
 
 class ROF_GCNConv(torch.nn.Module):

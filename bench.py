@@ -250,6 +250,7 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (tests / profiling only)")
     ap.add_argument("--no-pipeline", dest="pipeline", action="store_false",
                     help="N > 1: one all-gather, then the aggregation (no overlap)")
+    ap.add_argument("--schedule", default="", help="N > 1 pipeline stages as ring offsets, e.g. '0|1,2,3|4,5,6,7'")
     ap.add_argument("--tiles", default="auto", help="source tiles per pass on one GPU: auto or an integer")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -316,11 +317,16 @@ def main():
     ev = lambda: torch.cuda.Event(enable_timing=True)
     gather_events = []
     launches = [0]
-    tiles = (plan.auto_tiles(D) if args.tiles == "auto" else int(args.tiles)) if world == 1 else 1
+    if world == 1 or not args.pipeline:
+        tiles = plan.auto_tiles(D) if args.tiles == "auto" else int(args.tiles)
+    else:
+        tiles = 1                 # the pipeline's stages are already source-blocked
     pipes = {}
     if world > 1 and args.pipeline:
-        px = PipelinedAggregator(plan, feat_x)
-        pipes = {id(feat_x): px, id(feat_g): PipelinedAggregator(plan, feat_g, stage_plans=px.stage_plans)}
+        sched = [[int(k) for k in st.split(",")] for st in args.schedule.split("|")] if args.schedule else None
+        px = PipelinedAggregator(plan, feat_x, schedule=sched)
+        pipes = {id(feat_x): px,
+                 id(feat_g): PipelinedAggregator(plan, feat_g, stage_plans=px.stage_plans, schedule=sched)}
 
     def one_pass(p, src_loc, feat, out, timed_gather=False):
         if pipes and p is plan:       # all-gather rounds overlapped with the per-stage aggregation
@@ -485,6 +491,42 @@ def main():
                 sweep.append(row)
             del xs, o
         extra["sweep_forward_pass"] = sweep
+
+    # ---- one GCN layer through the drop-in layer API (informational: "GCN layer ms") -----------
+    if world == 1 and not args.no_sweep:
+        from artifact_b200.models import ROF_inputInfo
+        from artifact_b200.reuse_conv import ROF_GCNConv
+        f_in = {"c2": 602, "c4": 100, "c5": 64}[args.workload]
+        t = lambda k: i32(L[k]).to(dev)
+        info = ROF_inputInfo(None, None, deg, None, None, args.part_size, 4, None, None, None,
+                             t("uniqpart_column_index"), t("uniqpart_pointers"), t("part2Node_ptr"), t("part2Node_col"))
+        layer = ROF_GCNConv(f_in, D, add_self_loops=False, kernel_type="ROF_v2").to(dev)
+        xin = torch.randn((n, f_in), device=dev, requires_grad=True)
+
+        def layer_step():
+            y = layer(xin, info)
+            y.backward(feat_g.full[:n])
+            xin.grad = None; layer.zero_grad(set_to_none=True)
+
+        for _ in range(3):
+            layer_step()
+        s, e = ev(), ev()
+        s.record()
+        for _ in range(5):
+            layer_step()
+        e.record(); torch.cuda.synchronize()
+        ms_layer = s.elapsed_time(e) / 5
+        with torch.no_grad():
+            w_ = layer.weight.detach()
+            s.record()
+            for _ in range(5):
+                tmp = torch.mm(xin, w_); torch.mm(feat_g.full[:n], w_.t()); torch.mm(xin.t(), feat_g.full[:n])
+            e.record(); torch.cuda.synchronize()
+        ms_mm = s.elapsed_time(e) / 5
+        extra["gcn_layer"] = {"shape": [n, f_in, D], "kernel_type": "ROF_v2", "fwd_bwd_ms": round(ms_layer, 3),
+                              "of_which_dense_mm_ms": round(ms_mm, 3),
+                              "note": "ROF_GCNConv forward+backward; the three fp32 GEMMs (X.W, dX, dW) stay on cuBLAS"}
+        del info, layer, xin
 
     if rank == 0:
         cpu = None

@@ -109,3 +109,35 @@ def test_gcn_stack_trains_a_step_and_gin_runs():
     with torch.no_grad():
         out = gin(torch.randn((g3.num_nodes, 128), device=DEV), plan)
     assert out.shape == (g3.num_nodes, 40) and torch.isfinite(out).all()
+
+
+@pytest.mark.parametrize("kernel_type", ["GNNA", "ROF_v1", "ROF_v2"])
+def test_transposed_layouts_give_the_exact_gradient_on_a_directed_graph(kernel_type):
+    g = graphs.config2(500 / 232965)                     # directed: A_hat != A_hat^T
+    n = g.num_nodes
+    fwd = ROF_inputInfo.from_layouts(g.indptr_dst, search.search_graph(g, 2), device=DEV)
+    Lt = search.reuse_search(g.indptr_src, g.indices_dst, g.indptr_dst, g.indices_src, 2)   # the two CSRs swapped
+    bwd = ROF_inputInfo.from_layouts(g.indptr_src, Lt, device=DEV)
+    fwd.degrees = torch.clamp(fwd.degrees, min=1.0)
+    fwd.with_transposed(bwd)
+    A = torch.zeros((n, n), dtype=torch.float64)
+    A[np.repeat(np.arange(n), np.diff(g.indptr_dst)), g.indices_src] = 1.0
+    s = fwd.degrees.double().rsqrt().cpu()
+    A_hat = (s[:, None] * A * s[None, :]).to(DEV)
+    torch.manual_seed(3)
+    x = torch.randn((n, 12), device=DEV, requires_grad=True)
+    w = torch.randn((12, 8), device=DEV, requires_grad=True)
+    y = ROF_GCNConvFunc.apply(x, w, _with_cache(fwd, 8), False, kernel_type)
+    y.pow(2).sum().backward()
+    xd, wd = x.detach().double().requires_grad_(), w.detach().double().requires_grad_()
+    yd = A_hat @ (xd @ wd)
+    yd.pow(2).sum().backward()
+    assert_close(y.detach().cpu().numpy(), yd.detach().cpu().numpy(), rel=2e-5, what="forward")
+    assert_close(x.grad.cpu().numpy(), xd.grad.cpu().numpy(), rel=1e-4, abs_=1e-3, what="dX (exact, transposed)")
+    assert_close(w.grad.cpu().numpy(), wd.grad.cpu().numpy(), rel=1e-4, abs_=1e-2, what="dW (exact, transposed)")
+    # without the transposed layouts the backward is upstream's convention: the forward operator again
+    fwd.transposed = None
+    x2 = x.detach().clone().requires_grad_()
+    ROF_GCNConvFunc.apply(x2, w.detach(), _with_cache(fwd, 8), False, kernel_type).pow(2).sum().backward()
+    up = (A_hat @ (2 * yd.detach())) @ wd.detach().t()
+    assert_close(x2.grad.cpu().numpy(), up.cpu().numpy(), rel=1e-4, abs_=1e-3, what="dX (upstream convention)")
