@@ -9,7 +9,6 @@
 // fixed order, so the result is deterministic.  Work items are ordered longest first so the
 // hardware block scheduler balances the power-law tail.
 #include <algorithm>
-#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <numeric>
@@ -138,13 +137,13 @@ int finalize_plan(HostPlan& hp, rof_plan** out, cudaStream_t stream) {
 
   std::vector<WorkItem> items;
   std::vector<SplitRow> split;
-  // Segment length: at most kMaxSegmentEdges, shorter when the plan is small, so that there are
-  // always many more work items than resident warps (148 SMs x 32 warps): with 1024-entry
-  // segments a 14.5M-entry plan (one eighth of the 114.6M-edge graph) ran as two waves of
-  // segments and lost 25 % to the tail.
-  int seg = kMaxSegmentEdges;
-  while (seg > kMinSegmentEdges && entries / seg < kTargetSegments) seg /= 2;
-  if (const char* env = std::getenv("ROF_SEGMENT_EDGES")) seg = std::max(32, std::atoi(env));
+  // Segment length.  Long segments are cheaper (fewer segment sums to store and re-read, less
+  // per-item overhead: on the 114.6M-edge graph 8192-entry segments beat 256-entry ones by 18 %),
+  // but a small plan cut into long segments leaves SMs idle at the end (one eighth of that graph:
+  // 0.95 ms with 1024, 1.5 ms with 4096).  Aim at ~16k segments — a few per resident warp of
+  // a B200 (148 SMs x 32 warps) — rounded to a power of two within [256, 8192].
+  int seg = kMinSegmentEdges;
+  while (seg < kMaxSegmentEdges && (double)entries / kTargetSegments > 1.4142 * seg) seg *= 2;
   p->segment_edges = seg;
   items.reserve((size_t)rows + (size_t)(entries / seg) + 1);
   int slots = 0;

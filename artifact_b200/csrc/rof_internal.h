@@ -28,9 +28,9 @@ struct __align__(16) SplitRow {
   int32_t pad;
 };
 
-constexpr int kMaxSegmentEdges = 1024;   // longest run of entries one work item sums
-constexpr int kMinSegmentEdges = 128;
-constexpr int64_t kTargetSegments = 75000;  // ~16 work items per resident warp of a B200
+constexpr int kMaxSegmentEdges = 8192;   // longest run of entries one work item sums
+constexpr int kMinSegmentEdges = 256;
+constexpr double kTargetSegments = 16000.0;
 
 }  // namespace rof
 

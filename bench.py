@@ -38,7 +38,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one phase-B launch, from the ncu captures
 # summarised in profiles/gather_rows_<workload>_d<D>_<mode>.md (captured once per kernel change)
 NCU_DRAM_BYTES_PER_LAUNCH = {
-    "c2:D256:sum": 25.03e9,
+    "c2:D256:sum": 5.13e9,     # one pass = 4 source tiles x 1.28 GB (untiled: 25.03 GB)
     "c2:D64:sum": 1.44e9,
 }
 
@@ -174,8 +174,6 @@ def prepare_workload(args, rank, world):
     from artifact_b200 import graphs, search
     cache_dir = os.environ.get("ROF_CACHE_DIR", "/tmp/rof_b200_cache")
     path = os.path.join(cache_dir, f"{args.workload}_scale{args.scale}_ps{args.part_size}.npz")
-    t_graph = t_search = 0.0
-
     def compute():
         t0 = time.time()
         g = build_graph(args.workload, args.scale)
@@ -193,33 +191,38 @@ def prepare_workload(args, rank, world):
         L["original_column_index"] = g.indices_src
         return g, L
 
-    if os.path.exists(path):
-        try:
-            t0 = time.time()
-            g, L = load()
-            return g, L, time.time() - t0, 0.0
-        except Exception:
-            pass
+    # rank 0 makes sure the cache file exists (loading it, or computing and saving); every rank
+    # then passes the same barrier, and the other ranks load the file
     result = None
     if rank == 0:
-        g, L, t_graph, t_search = result = compute()
-        try:
-            os.makedirs(cache_dir, exist_ok=True)
-            tmp = path + f".tmp{os.getpid()}.npz"
-            np.savez(tmp, num_nodes=np.int64(g.num_nodes), symmetric=np.int64(g.symmetric), indptr_dst=g.indptr_dst,
-                     indices_src=g.indices_src, **{k: L[k] for k in _V2_KEYS})
-            os.replace(tmp, path)
-        except Exception:
-            pass
+        if os.path.exists(path):
+            try:
+                t0 = time.time()
+                g, L = load()
+                result = (g, L, time.time() - t0, 0.0)
+            except Exception:
+                result = None
+        if result is None:
+            result = compute()
+            g, L = result[0], result[1]
+            try:
+                os.makedirs(cache_dir, exist_ok=True)
+                tmp = path + f".tmp{os.getpid()}.npz"
+                np.savez(tmp, num_nodes=np.int64(g.num_nodes), symmetric=np.int64(g.symmetric),
+                         indptr_dst=g.indptr_dst, indices_src=g.indices_src, **{k: L[k] for k in _V2_KEYS})
+                os.replace(tmp, path)
+            except Exception:
+                pass
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
     if result is None:
         try:
+            t0 = time.time()
             g, L = load()
+            result = (g, L, time.time() - t0, 0.0)
         except Exception:
-            g, L, t_graph, t_search = compute()
-        return g, L, t_graph, t_search
+            result = compute()
     return result
 
 

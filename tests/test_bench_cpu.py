@@ -27,3 +27,37 @@ def test_non_zero_rank_of_reference_arm_is_silent():
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2",
                           "--scale", "0.01"], capture_output=True, text=True, env=env, timeout=120)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def _prep_worker(rank, world, port, cache_dir, q):
+    import argparse
+    import numpy as np
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), ROF_CACHE_DIR=cache_dir, OMP_NUM_THREADS="2")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    import bench
+    args = argparse.Namespace(workload="c5", scale=2048 / 1048576, part_size=2)
+    g, L, _, _ = bench.prepare_workload(args, rank, world)
+    q.put((rank, int(g.num_edges), int(np.asarray(L["uniqpart_column_index"]).sum()), len(L["picked_fanout"])))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_share_one_search_through_the_cache(tmp_path):
+    """rank 0 computes the workload and leaves it in the cache directory, rank 1 loads it: same arrays, no
+    deadlock whether the cache is cold or warm"""
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    for attempt in range(2):                                   # cold cache, then warm cache
+        q = ctx.Queue()
+        port = 29500 + (os.getpid() + 31 * attempt) % 2000
+        procs = [ctx.Process(target=_prep_worker, args=(r, 2, port, str(tmp_path), q)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got = sorted(q.get(timeout=180) for _ in range(2))
+        for p in procs:
+            p.join(timeout=60)
+            assert p.exitcode == 0
+        assert got[0][1:] == got[1][1:] and got[0][3] > 0
+    assert len(list(tmp_path.glob("*.npz"))) == 1

@@ -113,7 +113,7 @@ def _csr_as_parts(g, part_size):
 
 @pytest.mark.parametrize("mode", ["sum", "mean", "gcn"])
 def test_long_rows_are_split_and_reduced(mode):
-    """rows far beyond the 1024-entry segment limit (degree cap 20,000 in the benchmark graph)"""
+    """rows far beyond the segment limit (256 entries for a plan this small; degree cap 20,000 in the benchmark graph)"""
     g = graphs.config2(3000 / 232965)            # ~1.47M edges, max in-degree ~750 ... boost below
     n = g.num_nodes
     # add two very long rows: node 0 <- every node, node 1 <- every second node

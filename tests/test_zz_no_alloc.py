@@ -29,7 +29,7 @@ def reuse_plan():
 
 
 def long_row_plan(n=5000):
-    """two rows far beyond the 1024-entry segment limit: their segment sums live in the scratch"""
+    """two rows far beyond the segment limit (256 entries for a plan this small): their segment sums live in the scratch"""
     rows = [np.arange(n, dtype=np.int32), np.arange(0, n, 2, dtype=np.int32)] + \
            [np.array([(7 * v) % n, (11 * v + 3) % n], dtype=np.int32) for v in range(2, n)]
     ptr = np.concatenate([[0], np.cumsum([len(r) for r in rows])]).astype(np.int32)
