@@ -118,18 +118,21 @@ class PipelinedAggregator:
             self.ready.record(cur)
             with torch.cuda.stream(self.comm_stream):
                 self.comm_stream.wait_event(self.ready)
-                for s in range(1, len(self.schedule)):
+                for s in range(len(self.schedule)):
                     ops = []
                     for k in self.schedule[s]:
+                        if k == 0:
+                            continue                     # the rank's own block is already in place
                         src = (r + k) % R
                         ops.append(dist.P2POp(dist.isend, f.local_view(), (r - k) % R, group=f.group))
                         ops.append(dist.P2POp(dist.irecv, f.full[src * blk:(src + 1) * blk], src, group=f.group))
-                    for w in dist.batch_isend_irecv(ops):
-                        w.wait()
+                    if ops:
+                        for w in dist.batch_isend_irecv(ops):
+                            w.wait()
                     self.landed[s].record(self.comm_stream)
         self.launches = 0
         for s, p in enumerate(self.stage_plans):
-            if s:
+            if R > 1 and any(k != 0 for k in self.schedule[s]):
                 cur.wait_event(self.landed[s])
             p.aggregate(x_full, degrees, mode, out=out, accumulate=s > 0)
             self.launches += p.last_launch_count()

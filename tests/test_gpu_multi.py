@@ -42,7 +42,15 @@ def _worker(rank, world, port, name, q):
         for _ in range(3):                                 # repeated passes reuse buffers and events
             pipe.aggregate(local, deg, mode, out)
         torch.cuda.synchronize()
-        res[mode] = (a, out.cpu().numpy())
+        # a schedule whose first stage already needs peers' blocks
+        half = max(world // 2, 1)
+        out2 = torch.empty((r1 - r0, dim), device=dev)
+        pipe2 = PipelinedAggregator(plan, feats, schedule=[list(range(half)), list(range(half, world))])
+        feats.full.zero_()
+        for _ in range(2):
+            pipe2.aggregate(local, deg, mode, out2)
+        torch.cuda.synchronize()
+        res[mode] = (a, out.cpu().numpy(), out2.cpu().numpy())
     gathered = [None] * world
     dist.all_gather_object(gathered, (r0, res))
     if rank == 0:
@@ -80,3 +88,5 @@ def test_sharded_and_pipelined_match_oracle(name):
         piped = np.concatenate([r[mode][1] for _, r in sorted(gathered, key=lambda t: t[0])])
         assert_close(plain, want, what=f"all-gather then aggregate, {mode}")
         assert_close(piped, want, what=f"pipelined, {mode}")
+        piped2 = np.concatenate([r[mode][2] for _, r in sorted(gathered, key=lambda t: t[0])])
+        assert_close(piped2, want, what=f"pipelined, two half stages, {mode}")

@@ -72,3 +72,56 @@ def test_upstream_kernels_agree_with_oracle_and_new_kernels(name):
         assert_close(a.cpu().numpy(), b.cpu().numpy(), rel=2e-5, what=f"new {nm} vs upstream kernel")
     # upstream's caching kernel and ours fill the caller's cache alike (flag column included)
     assert_close(cache_new.cpu().numpy(), cache_up.cpu().numpy(), what="part_result_cache")
+
+
+def test_new_kernels_are_faster_than_upstream_kernels(capsys):
+    """times upstream's three kernels and the new path on the same B200 and inputs (a tenth of the
+    benchmark graph: upstream's layouts come from the product's search, which reproduces upstream's
+    preprocessor bit for bit) and prints the figures quoted in BASELINE.md"""
+    up = load_upstream()
+    if up is None:
+        pytest.skip("upstream CUDA extension not built (oracle/_ref/ROF_ref*.so)")
+    from artifact_b200 import graphs, search
+    g = graphs.config2(0.1)                      # 23,297 nodes, ~11.5M edges
+    L = search.search_graph(g, 2)
+    n, dim = g.num_nodes, 128
+    t = lambda a, dt=np.int32: torch.from_numpy(np.ascontiguousarray(a, dtype=dt)).to(DEV)
+    X = torch.randn((n, 64), device=DEV)
+    W = torch.randn((64, dim), device=DEV)
+    deg = t(np.maximum(g.degrees_f32(), 1.0), np.float32)
+    ci, pp, p2n = t(L["original_column_index"]), t(L["part_pointers"]), t(L["part2Node"])
+    v1 = [t(L[k]) for k in ("column_index", "part_pointers", "part2Node", "part_cache_flagindex",
+                            "part_pointers_cache", "column_index_cache")]
+    v2 = [t(L[k]) for k in ("uniqpart_column_index", "uniqpart_pointers", "part2Node_ptr", "part2Node_col")]
+    G = len(L["part_pointers_cache"]) - 1
+    cache = torch.zeros((G, dim + 1), device=DEV)
+    ps, dw, wpb = 2, 32, 4
+
+    def timed(fn, it=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(it):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / it
+
+    mm = timed(lambda: torch.mm(X, W))
+    res = {}
+    for name, mod in (("upstream", up), ("new", ops)):
+        res[name] = {
+            "GNNA": timed(lambda: mod.GNNA_forward(X, W, ci, deg, pp, p2n, ps, dw, wpb)) - mm,
+            "ROF_v1": timed(lambda: mod.reuse_forward_v1(X, W, v1[0], deg, v1[1], v1[2], ps, dw, wpb, cache, v1[3],
+                                                         v1[4], v1[5])) - mm,
+            "ROF_v2": timed(lambda: mod.reuse_forward_v2(X, W, v2[0], deg, v2[1], v2[2], v2[3], ps, dw, wpb)) - mm,
+        }
+    with capsys.disabled():
+        print(f"\n[upstream vs new, N={n} E={g.num_edges} D={dim}, forward aggregation ms (X.W {mm:.3f} ms excluded)]")
+        for k in ("GNNA", "ROF_v1", "ROF_v2"):
+            print(f"  {k}: upstream {res['upstream'][k]:.3f} ms, new {res['new'][k]:.3f} ms, "
+                  f"x{res['upstream'][k] / max(res['new'][k], 1e-6):.1f}")
+    for k in res["new"]:
+        assert res["new"][k] < res["upstream"][k]
