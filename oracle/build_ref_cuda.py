@@ -15,7 +15,9 @@ import sysconfig
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref", default="/root/reference")
+    here0 = os.path.dirname(os.path.abspath(__file__))
+    ap.add_argument("--ref", default=os.path.join(os.path.dirname(os.path.dirname(here0)), "reference"),
+                    help="upstream tree (default: the directory `reference` next to this repository)")
     args = ap.parse_args()
     here = os.path.dirname(os.path.abspath(__file__))
     src = os.path.join(args.ref, "ROF", "reuse_conv")

@@ -141,3 +141,29 @@ def test_transposed_layouts_give_the_exact_gradient_on_a_directed_graph(kernel_t
     ROF_GCNConvFunc.apply(x2, w.detach(), _with_cache(fwd, 8), False, kernel_type).pow(2).sum().backward()
     up = (A_hat @ (2 * yd.detach())) @ wd.detach().t()
     assert_close(x2.grad.cpu().numpy(), up.cpu().numpy(), rel=1e-4, abs_=1e-3, what="dX (upstream convention)")
+
+
+def test_gin_inference_matches_a_dense_fp64_model():
+    """3-layer GIN (sum aggregation, eps = 0, 2-layer MLPs) on a symmetrised power-law graph"""
+    g = graphs.config3(1500 / 169343)
+    n = g.num_nodes
+    L = search.search_graph(g, 3)
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)
+    plan = AggregationPlan.from_v2(n, i32(L["uniqpart_column_index"]), i32(L["uniqpart_pointers"]),
+                                   i32(L["part2Node_ptr"]), i32(L["part2Node_col"]))
+    torch.manual_seed(4)
+    gin = ROF_GIN(128, 256, 40, 3, eps=0.0).to(DEV)
+    x = torch.randn((n, 128), device=DEV)
+    with torch.no_grad():
+        got = gin(x, plan).cpu().numpy()
+    A = np.zeros((n, n))
+    A[np.repeat(np.arange(n), np.diff(g.indptr_dst)), g.indices_src] = 1.0
+    h = x.cpu().numpy().astype(np.float64)
+    for i, mlp in enumerate(gin.mlps):
+        z = h + A @ h
+        w1, b1 = mlp[0].weight.detach().cpu().numpy().astype(np.float64), mlp[0].bias.detach().cpu().numpy()
+        w2, b2 = mlp[2].weight.detach().cpu().numpy().astype(np.float64), mlp[2].bias.detach().cpu().numpy()
+        h = np.maximum(z @ w1.T + b1, 0.0) @ w2.T + b2
+        if i + 1 < len(gin.mlps):
+            h = np.maximum(h, 0.0)
+    assert_close(got, h, rel=1e-4, abs_=1e-4, what="GIN logits")

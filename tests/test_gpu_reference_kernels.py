@@ -77,7 +77,7 @@ def test_upstream_kernels_agree_with_oracle_and_new_kernels(name):
 def test_new_kernels_are_faster_than_upstream_kernels(capsys):
     """times upstream's three kernels and the new path on the same B200 and inputs (a tenth of the
     benchmark graph: upstream's layouts come from the product's search, which reproduces upstream's
-    preprocessor bit for bit) and prints the figures quoted in BASELINE.md"""
+    preprocessor bit for bit) and prints both sets of timings"""
     up = load_upstream()
     if up is None:
         pytest.skip("upstream CUDA extension not built (oracle/_ref/ROF_ref*.so)")

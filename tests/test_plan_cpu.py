@@ -130,3 +130,30 @@ def test_bad_arguments():
     assert e.value.status == 1
     with pytest.raises(TypeError):
         AggregationPlan.from_parts(4, np.zeros(2, np.float32), z, z)
+
+
+def test_auto_tiles_heuristic():
+    """source tiling only when the feature matrix exceeds L2 and rows stay long per tile"""
+    from conftest import load_golden
+    g = load_golden("c2_n640_ps2")                      # 640 nodes, mean degree ~160
+    plan = AggregationPlan.from_parts(g["N"], *layout_args(g["layouts"], "parts"))
+    assert plan.auto_tiles(256) == 1                    # 640 x 256 x 4 B is far below L2
+    # the same row length on a matrix of 10^6 rows x 256: tiles until ~64 MB blocks, at most 8,
+    # but never fewer than 48 entries per row and tile
+    plan.info = dict(plan.info, num_nodes=1_000_000, row_begin=0, row_end=1000, gather_entries=1000 * 160)
+    assert plan.auto_tiles(256) == 2
+    plan.info = dict(plan.info, gather_entries=1000 * 2000)
+    assert plan.auto_tiles(256) == 8
+    plan.info = dict(plan.info, gather_entries=1000 * 40)
+    assert plan.auto_tiles(256) == 1
+    assert plan.auto_tiles(16) == 1
+
+
+def test_segment_length_follows_plan_size():
+    z = np.zeros(0, np.int32)
+    n = 300
+    big = np.arange(n, dtype=np.int32)
+    col = np.concatenate([big] * 3)                     # three rows of 300 entries
+    plan = AggregationPlan.from_parts(n, col, np.array([0, 300, 600, 900], np.int32), np.array([0, 1, 2], np.int32))
+    assert plan.info["segment_edges"] == 256            # small plan: shortest segments
+    assert plan.info["split_rows"] == 3 and plan.info["num_slots"] == 6
