@@ -22,6 +22,8 @@
 // tests/test_search_cpu.py checks every output array against upstream's own module.
 #include <algorithm>
 #include <cstdint>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <numeric>
 #include <parallel/algorithm>
@@ -56,7 +58,7 @@ void build_bitmaps(const Csr& out, int64_t budget_bytes, Bitmaps& bm) {
   int64_t max_maps = per > 0 ? budget_bytes / per : 0;
   if (max_maps <= 0) return;
   // a bitmap pays off only when the list is long relative to a probe/merge
-  const int64_t min_deg = std::max<int64_t>(64, bm.words / 16);
+  const int64_t min_deg = std::max<int64_t>(256, bm.words / 4);
   std::vector<int32_t> cand;
   for (int v = 0; v < n; ++v)
     if (out.deg(v) >= min_deg) cand.push_back(v);
@@ -128,6 +130,17 @@ int64_t intersect_part(const Csr& out, const Bitmaps& bm, const int32_t* src, in
     len[i] = out.deg(s);
   }
   int64_t cnt = 0;
+  bool others_mapped = true;
+  for (int i = 1; i < ps; ++i) others_mapped &= (maps[i] != nullptr);
+  if (!out_list && others_mapped) {  // count only, every other list as a bitmap: branch-free probes
+    for (int64_t k = 0; k < d0; ++k) {
+      const int32_t u = a[k];
+      uint64_t bit = 1;
+      for (int i = 1; i < ps; ++i) bit &= maps[i][u >> 6] >> (u & 63);
+      cnt += (int64_t)(bit & 1);
+    }
+    return cnt;
+  }
   for (int64_t k = 0; k < d0; ++k) {
     const int32_t u = a[k];
     bool in_all = true;
@@ -220,29 +233,40 @@ rofh_search* rofh_reuse_search(int n, const int64_t* indptr_dst, const int32_t* 
   // ---- get_part_intersect (sizes only; discard_remainder_part = true) ------------------
   Bitmaps bm;
   build_bitmaps(outg, bitmap_budget_bytes, bm);
+  if (std::getenv("ROFH_TRACE")) fprintf(stderr, "[search] bitmaps %.2fs\n", omp_get_wtime() - t0);
   std::vector<int32_t>& nums = S->arr[ROFH_INTERSECTION_NUM];
   nums.assign((size_t)P, 0);
   {
     // Many parts hold the same source tuple (hub pairs recur in thousands of rows) and the
     // expensive ones are exactly those: count each distinct tuple once.  Parts are grouped
-    // by sorting (hash of tuple, part id); equal hashes are confirmed by comparing tuples.
+    // by sorting a 64-bit key (highest-out-degree source of the tuple, 32-bit hash of the
+    // tuple): equal tuples become neighbours (confirmed by comparing the tuples), and
+    // consecutive tuples share their longest out-list, which then stays in cache.
     struct Key { uint64_t h; u32 p; bool operator<(const Key& o) const { return h < o.h || (h == o.h && p < o.p); } };
-    std::vector<Key> keys;
-    keys.reserve((size_t)P);
-    for (int64_t p = 0; p < P; ++p)
-      if (part_ptr[(size_t)p + 1] - part_ptr[(size_t)p] == ps) keys.push_back(Key{0, (u32)p});
-    const int64_t F = (int64_t)keys.size();
+    std::vector<Key> keys((size_t)P);
 #pragma omp parallel for schedule(static, 4096)
-    for (int64_t i = 0; i < F; ++i) {
-      const int32_t* t = indices_src + part_ptr[keys[(size_t)i].p];
+    for (int64_t p = 0; p < P; ++p) {
+      if (part_ptr[(size_t)p + 1] - part_ptr[(size_t)p] != ps) {
+        keys[(size_t)p] = Key{~0ull, (u32)p};  // partial parts sort to the end and are dropped
+        continue;
+      }
+      const int32_t* t = indices_src + part_ptr[(size_t)p];
       uint64_t h = 0x9E3779B97F4A7C15ull;
+      int32_t big = t[0];
       for (int k = 0; k < ps; ++k) {
         h ^= (uint64_t)(u32)t[k] + 0x9E3779B97F4A7C15ull + (h << 6) + (h >> 2);
         h *= 0xBF58476D1CE4E5B9ull;
+        if (outg.deg(t[k]) > outg.deg(big)) big = t[k];
       }
-      keys[(size_t)i].h = h;
+      keys[(size_t)p] = Key{((uint64_t)(u32)big << 32) | (h >> 32), (u32)p};
     }
+    if (std::getenv("ROFH_TRACE")) fprintf(stderr, "[search] keys %.2fs\n", omp_get_wtime() - t0);
     __gnu_parallel::sort(keys.begin(), keys.end());
+    while (!keys.empty() && keys.back().h == ~0ull &&
+           part_ptr[(size_t)keys.back().p + 1] - part_ptr[(size_t)keys.back().p] != ps)
+      keys.pop_back();
+    const int64_t F = (int64_t)keys.size();
+    if (std::getenv("ROFH_TRACE")) fprintf(stderr, "[search] sorted %.2fs\n", omp_get_wtime() - t0);
     auto same_tuple = [&](u32 a, u32 b) {
       return std::memcmp(indices_src + part_ptr[a], indices_src + part_ptr[b], sizeof(int32_t) * (size_t)ps) == 0;
     };
@@ -279,11 +303,19 @@ rofh_search* rofh_reuse_search(int n, const int64_t* indptr_dst, const int32_t* 
   // The same call upstream makes (:245-264): std::sort over an identity permutation of
   // uint32 with this comparator.  Ties are broken by the library's introsort; making the
   // identical call on identical data is what reproduces upstream's order.
+  // std::sort's result depends only on the outcomes of its comparisons, so sorting
+  // (fan-out, index) pairs by fan-out walks through the same comparisons and moves as upstream's
+  // sort of bare indices with a look-up comparator, without the cache miss per comparison.
+  struct Keyed { u32 num; u32 idx; };
   std::vector<u32> unums(nums.begin(), nums.end());
+  std::vector<Keyed> keyed((size_t)P);
+#pragma omp parallel for schedule(static, 1 << 16)
+  for (int64_t i = 0; i < P; ++i) keyed[(size_t)i] = Keyed{unums[(size_t)i], (u32)i};
+  std::sort(keyed.begin(), keyed.end(), [](const Keyed& a, const Keyed& b) { return a.num > b.num; });
   std::vector<u32> index_ordered((size_t)P);
-  std::iota(index_ordered.begin(), index_ordered.end(), 0u);
-  std::sort(index_ordered.begin(), index_ordered.end(),
-            [&unums](size_t i1, size_t i2) { return unums[i1] > unums[i2]; });
+#pragma omp parallel for schedule(static, 1 << 16)
+  for (int64_t i = 0; i < P; ++i) index_ordered[(size_t)i] = keyed[(size_t)i].idx;
+  keyed.clear(); keyed.shrink_to_fit();
   std::vector<int32_t>& picked = S->arr[ROFH_INDEX_PICKED];
   std::vector<uint8_t> taken((size_t)n, 0);
   for (int64_t i = 0; i < P; ++i) {

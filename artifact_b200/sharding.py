@@ -61,20 +61,22 @@ class ShardedAggregator:
         return self.plan.aggregate(x_full, degrees, mode, out=out, phases=phases)
 
 
-def stage_schedule(world, first=3, growth=3):
-    """Which peers' blocks travel in which stage: stage 0 is the rank's own block, the next stage
-    fetches `first` peer blocks and each later one `growth` times as many as the one before, so the
-    aggregation of one stage covers the transfer of the next, and the number of stages (kernel
-    launches and NCCL calls per pass) grows with log(world), not world.  Returns a list of lists
-    of ring offsets k (the block of rank (r + k) % world): [[0], [1, 2, 3], [4, 5, 6, 7]] for 8
-    ranks.  Measured at 8 x B200 on the 114.6M-edge graph, D=256, ms per forward+backward step:
-    [[0],[1,2,3],[4..7]] 2.57; [[0],[1..7]] 2.66; no overlap 2.77; [[0,1,2,3],[4..7]] 2.77;
-    [[0],[1],[2,3,4],[5,6,7]] 3.03; one stage per peer 5.7 (launch-bound)."""
-    stages, k, size = [[0]], 1, first
-    while k < world:
-        stages.append(list(range(k, min(world, k + size))))
-        k += size
-        size *= growth
+def stage_schedule(world):
+    """Which peers' blocks travel in which stage, as lists of ring offsets k (the block of rank
+    (r + k) % world).  Stage 0 is the rank's own block; the peers are cut into two groups, the
+    nearer (world-1)//2 first, so that a pass is three stages whatever the world size: the
+    aggregation of one stage covers the transfer of the next, while the number of kernel launches
+    and NCCL calls per pass stays fixed.  [[0], [1, 2, 3], [4, 5, 6, 7]] for 8 ranks, [[0], [1],
+    [2, 3]] for 4.  Measured on B200s, 114.6M-edge graph, D=256, ms per forward+backward step —
+    8 GPUs: [[0],[1,2,3],[4..7]] 2.57; [[0],[1..7]] 2.66; no overlap 2.77; [[0,1,2,3],[4..7]] 2.77;
+    [[0],[1],[2,3,4],[5,6,7]] 3.03; one stage per peer 5.7 (launch-bound);
+    4 GPUs: [[0],[1],[2,3]] 3.63; [[0],[1,2,3]] 3.96."""
+    if world <= 1:
+        return [[0]]
+    first = max(1, (world - 1) // 2)
+    stages = [[0], list(range(1, 1 + first))]
+    if 1 + first < world:
+        stages.append(list(range(1 + first, world)))
     return stages
 
 

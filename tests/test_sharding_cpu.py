@@ -91,5 +91,6 @@ def test_stage_schedule_covers_every_peer_once():
         assert sch[0] == [0]
         flat = [k for s in sch for k in s]
         assert flat == list(range(w))
-        assert len(sch) <= 2 + int(np.ceil(np.log(max(w, 1)) / np.log(3)))
+        assert len(sch) <= 3
     assert stage_schedule(8) == [[0], [1, 2, 3], [4, 5, 6, 7]] and stage_schedule(2) == [[0], [1]]
+    assert stage_schedule(4) == [[0], [1], [2, 3]]
