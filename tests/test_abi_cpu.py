@@ -33,3 +33,22 @@ def test_version_and_error_string():
 def test_host_library_loads():
     lib = _native.host()
     assert hasattr(lib, "rofh_chung_lu_rows") and hasattr(lib, "rofh_symmetrize")
+
+
+def test_header_is_plain_c(tmp_path):
+    """the boundary is a C ABI: the header must compile as C99 on its own, and a C program that
+    names every function must link against the library"""
+    import subprocess
+    hdr = os.path.join(ROOT, "include", "rof_b200.h")
+    subprocess.check_call(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-x", "c", hdr])
+    src = tmp_path / "use_all.c"
+    names = declared_functions()
+    src.write_text('#include "rof_b200.h"\n#include <stdio.h>\nint main(void) {\n  const void* f[] = {' +
+                   ", ".join(f"(const void*){n}" for n in names) +
+                   '};\n  printf("%d %d\\n", (int)(sizeof f / sizeof f[0]), rof_compiled_arch());\n  return rof_version() > 0 ? 0 : 1;\n}\n')
+    exe = tmp_path / "use_all"
+    libdir = os.path.dirname(build.cuda_lib_path())
+    subprocess.check_call(["gcc", "-std=c99", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe),
+                           "-L", libdir, "-lrof_b200", f"-Wl,-rpath,{libdir}", "-Wl,-rpath,/usr/local/cuda/lib64"])
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0 and out.stdout.split() == [str(len(names)), "100"]
