@@ -5,6 +5,7 @@ ROF_evaluation/ROF_main.py:164-174) and then drives every aggregation pass.  tor
 only to allocate device memory and to name the current stream.
 """
 import ctypes
+import os
 
 import numpy as np
 import torch
@@ -12,6 +13,9 @@ import torch
 from . import _native
 
 MODES = {"gcn": 0, "sum": 1, "mean": 2}
+_PHASE_NAMES = {1: "rof:partials", 2: "rof:gather", 4: "rof:segment_reduce", 7: "rof:aggregate"}
+# ROF_NVTX=1 brackets every C-ABI aggregation call with an NVTX range (visible to ncu --nvtx)
+_NVTX = os.environ.get("ROF_NVTX", "0") not in ("", "0")
 ON_HOST, ON_DEVICE = 0, 1
 
 
@@ -257,11 +261,17 @@ class AggregationPlan:
                 if gather_events is not None and ph & 2:
                     e0 = torch.cuda.Event(enable_timing=True)
                     e0.record()
-                _native.check(lib.rof_aggregate_phases(
-                    self._h, ph | (8 if accumulate else 0), m, ctypes.c_void_p(x.data_ptr()), ldx, dim, deg_ptr,
-                    ctypes.c_void_p(out.data_ptr()), ldo, cache_ptr,
-                    ctypes.c_void_p(ws.data_ptr()) if ws is not None else None, ws.numel() if ws is not None else 0,
-                    stream))
+                if _NVTX:
+                    torch.cuda.nvtx.range_push(_PHASE_NAMES.get(ph, "rof:phases"))
+                try:
+                    _native.check(lib.rof_aggregate_phases(
+                        self._h, ph | (8 if accumulate else 0), m, ctypes.c_void_p(x.data_ptr()), ldx, dim, deg_ptr,
+                        ctypes.c_void_p(out.data_ptr()), ldo, cache_ptr,
+                        ctypes.c_void_p(ws.data_ptr()) if ws is not None else None,
+                        ws.numel() if ws is not None else 0, stream))
+                finally:
+                    if _NVTX:
+                        torch.cuda.nvtx.range_pop()
                 self.launches += int(lib.rof_last_launch_count())
                 if gather_events is not None and ph & 2:
                     e1 = torch.cuda.Event(enable_timing=True)

@@ -81,3 +81,54 @@ def reuse_ratios(layouts):
         "reused_edge_ratio": float(fan.sum() * ps / max(raw_edges, 1)),
         "reused_edge_reduction_ratio": float((fan - 1).sum() * ps / max(raw_edges, 1)),
     }
+
+
+# ---- on-disk cache of search results -------------------------------------------------------
+# The search takes tens of seconds at 10^8 edges (upstream's own takes hours), so its outputs
+# are worth keeping between runs, like upstream's scripts keep their `inputInfo` with
+# torch.save (ROF_evaluation/cuda/middle-main.py:440-452).  One .npz per (graph, part_size);
+# the graph is identified by its shape and a digest of its CSR.
+
+_SAVED = _ARRAYS + ["original_column_index"]
+
+
+def graph_digest(indptr_dst, indices_src):
+    import hashlib
+    h = hashlib.sha256()
+    ip = np.ascontiguousarray(indptr_dst, dtype=np.int64)
+    ix = np.ascontiguousarray(indices_src, dtype=np.int32)
+    h.update(np.int64([ip.shape[0], ix.shape[0]]).tobytes())
+    h.update(ip.tobytes())
+    h.update(ix.tobytes())
+    return h.hexdigest()[:24]
+
+
+def save_layouts(path, layouts):
+    tmp = f"{path}.tmp{os.getpid()}.npz"
+    np.savez(tmp, part_size=np.int64(layouts["part_size"]), **{k: layouts[k] for k in _SAVED})
+    os.replace(tmp, path)
+
+
+def load_layouts(path):
+    z = np.load(path)
+    out = {k: z[k] for k in _SAVED}
+    out["part_size"] = int(z["part_size"])
+    out["seconds"] = {}
+    return out
+
+
+def cached_search_graph(g, part_size, cache_dir, **kw):
+    """search_graph() with results kept under `cache_dir`; returns (layouts, was_cached)."""
+    os.makedirs(cache_dir, exist_ok=True)
+    path = os.path.join(cache_dir, f"reuse_{graph_digest(g.indptr_dst, g.indices_src)}_ps{int(part_size)}.npz")
+    if os.path.exists(path):
+        try:
+            return load_layouts(path), True
+        except Exception:
+            pass                                            # unreadable file: recompute and overwrite
+    L = search_graph(g, part_size, **kw)
+    try:
+        save_layouts(path, L)
+    except OSError:
+        pass
+    return L, False

@@ -61,3 +61,15 @@ def test_bad_arguments():
         search.search_graph(g, 0)
     with pytest.raises(ValueError):
         search.reuse_search(g.indptr_dst, g.indices_src[::-1].copy(), g.indptr_src, g.indices_dst, 2)
+
+
+def test_cached_search_round_trips(tmp_path):
+    g = graphs.config5(2048 / 1048576)
+    a, hit_a = search.cached_search_graph(g, 2, str(tmp_path))
+    b, hit_b = search.cached_search_graph(g, 2, str(tmp_path))
+    assert (hit_a, hit_b) == (False, True)
+    compare(a, b)
+    assert b["part_size"] == 2 and np.array_equal(b["original_column_index"], g.indices_src)
+    g2 = graphs.config5(4096 / 1048576)                    # another graph: another cache entry
+    _, hit_c = search.cached_search_graph(g2, 2, str(tmp_path))
+    assert not hit_c and len(list(tmp_path.glob("reuse_*_ps2.npz"))) == 2

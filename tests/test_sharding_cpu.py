@@ -94,3 +94,36 @@ def test_stage_schedule_covers_every_peer_once():
         assert len(sch) <= 3
     assert stage_schedule(8) == [[0], [1, 2, 3], [4, 5, 6, 7]] and stage_schedule(2) == [[0], [1]]
     assert stage_schedule(4) == [[0], [1], [2, 3]]
+
+
+def _lonely_worker(rank, world, port, q):
+    import datetime
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    from artifact_b200.sharding import ShardedFeatures
+    feats = ShardedFeatures(64, 4, rank, world, torch.device("cpu"))
+    feats.all_gather(torch.ones((feats.block, 4)))          # a pass with every rank present works
+    dist.barrier()
+    if rank == 1:
+        os._exit(0)                                         # rank 1 leaves between passes, nothing in flight
+    try:
+        feats.all_gather(torch.ones((feats.block, 4)))
+        q.put("no error")
+    except Exception as e:                                  # the survivor gets an error, not a hang
+        q.put(type(e).__name__)
+
+
+def test_a_rank_that_left_is_an_error_not_a_hang():
+    """failure detection is the process group's: a pass after a peer has gone ends with an
+    exception within the group's timeout (the device code itself never waits on a peer)"""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() * 3 + 17) % 2000
+    procs = [ctx.Process(target=_lonely_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+    assert got != "no error", got
