@@ -81,6 +81,9 @@ CUDA_ABI = [
                               c_void_p, c_int64, c_void_p]),
     ("rof_aggregate_phases", c_int, [c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64,
                                      c_void_p, c_void_p, c_int64, c_void_p]),
+    ("rof_aggregate_fused", c_int, [c_void_p, c_int, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64,
+                                    c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, ctypes.c_float, c_int,
+                                    c_void_p]),
     ("rof_aggregate_static_scratch", c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64,
                                              c_void_p]),
     ("rof_last_launch_count", c_int, []),

@@ -63,7 +63,17 @@ int rof_aggregate(const rof_plan* p, int mode, const float* x, int64_t ldx, int 
 int rof_aggregate_phases(const rof_plan* p, int phases, int mode, const float* x, int64_t ldx, int dim,
                          const float* degrees, float* out, int64_t ldo, float* cache_result,
                          void* workspace, int64_t workspace_bytes, void* stream_) {
+  return rof_aggregate_fused(p, phases, mode, x, ldx, dim, degrees, out, ldo, cache_result, workspace, workspace_bytes,
+                             nullptr, nullptr, 0, 0.0f, 0, stream_);
+}
+
+int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x, int64_t ldx, int dim,
+                        const float* degrees, float* out, int64_t ldo, float* cache_result,
+                        void* workspace, int64_t workspace_bytes, const float* bias, const float* self_x,
+                        int64_t ld_self, float self_scale, int relu, void* stream_) {
   g_last_launches = 0;
+  if (self_x != nullptr && ld_self < dim) { set_error("rof_aggregate_fused: ld_self < dim"); return ROF_ERR_BAD_ARGUMENT; }
+  const Epilogue ep{bias, self_x, ld_self, self_scale, relu ? 1 : 0};
   if (phases & ~(ROF_PHASE_ALL | ROF_PHASE_ACCUMULATE)) { set_error("rof_aggregate_phases: unknown phase bit"); return ROF_ERR_BAD_ARGUMENT; }
   const int accumulate = (phases & ROF_PHASE_ACCUMULATE) ? 1 : 0;
   cudaStream_t stream = (cudaStream_t)stream_;
@@ -114,6 +124,7 @@ int rof_aggregate_phases(const rof_plan* p, int phases, int mode, const float* x
     a.mirror = nullptr; a.ldm = 0; a.mirror_flag_col = -1;
     a.num_nodes = p->num_nodes; a.row_begin = p->row_begin; a.dim = dim; a.weight_gcn = gcn; a.scale_mode = scale_mode;
     a.accumulate = accumulate;
+    a.ep = ep;
     e = launch_gather(a, stream);
     if (e != cudaSuccess) return cuda_fail(e, "phase B (destination gather)");
     g_last_launches += (dim + 2047) / 2048;
@@ -123,6 +134,7 @@ int rof_aggregate_phases(const rof_plan* p, int phases, int mode, const float* x
     r.rows = p->d_split; r.num_rows = p->num_split_rows; r.slots = slots; r.lds = w.ld; r.degrees = degrees;
     r.out = out; r.ldo = ldo; r.row_begin = p->row_begin; r.dim = dim; r.scale_mode = scale_mode;
     r.accumulate = accumulate;
+    r.ep = ep;
     e = launch_split_reduce(r, stream);
     if (e != cudaSuccess) return cuda_fail(e, "segment reduce");
     g_last_launches += 1;

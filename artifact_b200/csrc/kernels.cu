@@ -49,6 +49,25 @@ __device__ __forceinline__ void store_row_vec(float* p, const float (&v)[VEC]) {
   }
 }
 
+// out = act(r + self_scale * self_x[row][col..] + bias[col..]) for VEC consecutive columns.
+// The pointers need no alignment: the epilogue reads scalars.
+template <int VEC>
+__device__ __forceinline__ void apply_epilogue(float (&r)[VEC], const Epilogue& ep, int row, int col) {
+  if (ep.self_x != nullptr) {
+    const float* sp = ep.self_x + (int64_t)row * ep.ld_self + col;
+#pragma unroll
+    for (int t = 0; t < VEC; ++t) r[t] = __fmaf_rn(ep.self_scale, __ldg(sp + t), r[t]);
+  }
+  if (ep.bias != nullptr) {
+#pragma unroll
+    for (int t = 0; t < VEC; ++t) r[t] = __fadd_rn(r[t], __ldg(ep.bias + col + t));
+  }
+  if (ep.relu) {
+#pragma unroll
+    for (int t = 0; t < VEC; ++t) r[t] = fmaxf(r[t], 0.0f);
+  }
+}
+
 // acc += sum over col[begin, end) of (WEIGHTED ? rsqrt(degrees[c]) : 1) * row(c), where
 // row(c) starts at base_lane + (c - c_offset) * ld (base_lane already includes this lane's
 // column offset).  `active[k]` says whether this lane's k-th vector lies inside the row.
@@ -192,6 +211,7 @@ __global__ void __launch_bounds__(256, (C <= 2 ? 4 : 1)) gather_rows_kernel(cons
 #pragma unroll
         for (int t = 0; t < VEC; ++t) r[t] = __fadd_rn(prev[t], r[t]);
       }
+      if (dst >= 0) apply_epilogue<VEC>(r, a.ep, dst, iv * VEC);
       store_row_vec<VEC>(op + (int64_t)iv * VEC, r);
       if (a.mirror != nullptr && dst >= 0) {
         float* mp = a.mirror + (int64_t)dst * a.ldm + (int64_t)iv * VEC;
@@ -222,8 +242,10 @@ __global__ void __launch_bounds__(256) split_reduce_kernel(const ReduceArgs a) {
   for (int d = lane; d < a.dim; d += 32) {
     float s = 0.0f;
     for (int k = 0; k < count; ++k) s = __fadd_rn(s, a.slots[(int64_t)(first + k) * a.lds + d]);
-    const float r = __fmul_rn(s, scale);
-    op[d] = a.accumulate ? __fadd_rn(op[d], r) : r;
+    float r[1] = {__fmul_rn(s, scale)};
+    if (a.accumulate) r[0] = __fadd_rn(op[d], r[0]);
+    apply_epilogue<1>(r, a.ep, row, d);
+    op[d] = r[0];
   }
 }
 
@@ -292,6 +314,8 @@ cudaError_t launch_gather(const GatherArgs& a0, cudaStream_t stream) {
     if (a0.partials) a.partials = a0.partials + off;
     if (a0.out) a.out = a0.out + off;
     if (a0.slots) a.slots = a0.slots + off;
+    if (a0.ep.bias) a.ep.bias = a0.ep.bias + off;
+    if (a0.ep.self_x) a.ep.self_x = a0.ep.self_x + off;
     if (a0.mirror) {
       a.mirror = a0.mirror + off;
       // the 1.0 "ready" flag sits after the last column: only the last tile writes it

@@ -83,6 +83,15 @@ struct HostPlan {
 
 int finalize_plan(HostPlan& hp, rof_plan** out, cudaStream_t stream);
 
+// Optional fused epilogue of a final output row: out = act(result + self_scale * self_x[row] + bias)
+struct Epilogue {
+  const float* bias;     // [dim] or null
+  const float* self_x;   // [num_nodes, ld_self] rows addressed by global row id, or null
+  int64_t ld_self;
+  float self_scale;
+  int relu;
+};
+
 struct GatherArgs {
   const WorkItem* items;
   int num_items;
@@ -100,6 +109,7 @@ struct GatherArgs {
   int weight_gcn;   // multiply each feature row by rsqrt(degrees[col])
   int scale_mode;   // 0 none, 1 rsqrt(degrees[dst]), 2 1/degrees[dst]
   int accumulate;   // dst >= 0 rows: out += result instead of out = result
+  Epilogue ep;      // applied to dst >= 0 rows after scaling (and accumulating)
 };
 
 struct ReduceArgs {
@@ -112,6 +122,7 @@ struct ReduceArgs {
   int dim;
   int scale_mode;
   int accumulate;
+  Epilogue ep;
 };
 
 // Launchers (kernels.cu).  Return cudaSuccess or the launch error.

@@ -87,6 +87,11 @@ class ROF_GCN(torch.nn.Module):
 
     def forward(self, features, inputInfo, edge_index=None):
         h = features
+        if not torch.is_grad_enabled() and self.activation is F.relu:
+            # inference: bias and ReLU are fused into the store of the gather kernel
+            for i, layer in enumerate(self.layers):
+                h = layer.forward_fused(h, inputInfo, relu=i + 1 < len(self.layers))
+            return h
         for i, layer in enumerate(self.layers):
             if i:
                 h = F.dropout(h, self.dropout, self.training)
@@ -97,17 +102,23 @@ class ROF_GCN(torch.nn.Module):
 
 
 class SumAggregate(torch.autograd.Function):
-    """h -> A h (sum or mean over in-neighbours) through an AggregationPlan; the backward pass
-    applies the transposed plan when given one, else the same plan (upstream's convention)."""
+    """h -> self_scale * h + A h (sum or mean over in-neighbours) through an AggregationPlan, the
+    self term fused into the store of the gather kernel.  The backward pass applies the
+    transposed plan when given one, else the same plan (upstream's convention), with the same
+    fused self term."""
 
     @staticmethod
-    def forward(ctx, h, plan, plan_t, degrees, mode):
-        ctx.plan_t, ctx.degrees, ctx.mode = (plan_t or plan), degrees, mode
-        return plan.aggregate(h.contiguous(), degrees, mode, tiles="auto")
+    def forward(ctx, h, plan, plan_t, degrees, mode, self_scale=0.0):
+        ctx.plan_t, ctx.degrees, ctx.mode, ctx.self_scale = (plan_t or plan), degrees, mode, self_scale
+        h = h.contiguous()
+        return plan.aggregate(h, degrees, mode, tiles="auto", self_x=h if self_scale else None,
+                              self_scale=self_scale)
 
     @staticmethod
     def backward(ctx, g):
-        return ctx.plan_t.aggregate(g.contiguous(), ctx.degrees, ctx.mode, tiles="auto"), None, None, None, None
+        g = g.contiguous()
+        return (ctx.plan_t.aggregate(g, ctx.degrees, ctx.mode, tiles="auto", self_x=g if ctx.self_scale else None,
+                                     self_scale=ctx.self_scale), None, None, None, None, None)
 
 
 class ROF_GIN(torch.nn.Module):
@@ -124,8 +135,7 @@ class ROF_GIN(torch.nn.Module):
     def forward(self, features, plan: AggregationPlan, plan_t=None):
         h = features
         for i, mlp in enumerate(self.mlps):
-            agg = SumAggregate.apply(h, plan, plan_t, None, "sum")
-            h = mlp((1.0 + self.eps) * h + agg)
+            h = mlp(SumAggregate.apply(h, plan, plan_t, None, "sum", 1.0 + self.eps))
             if i + 1 < len(self.mlps):
                 h = F.relu(h)
         return h

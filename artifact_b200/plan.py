@@ -199,20 +199,26 @@ class AggregationPlan:
         return tp
 
     def aggregate(self, x, degrees=None, mode="gcn", out=None, cache_result=None, workspace=None, phases=7,
-                  accumulate=False, tiles=1, gather_events=None):
+                  accumulate=False, tiles=1, gather_events=None, bias=None, self_x=None, self_scale=1.0,
+                  relu=False):
         """out[v] = scale(v) * sum over v's gathered rows; see rof_aggregate() in include/rof_b200.h.
         `x` is [num_nodes, dim] fp32 on the GPU; returns a new [rows, dim] tensor unless `out` is given.
         tiles: 1 = one pass over the whole plan; N > 1 or "auto" = N source tiles (see auto_tiles).
-        gather_events: optional list; (start, stop) CUDA events around every phase-B launch are appended."""
+        gather_events: optional list; (start, stop) CUDA events around every phase-B launch are appended.
+        bias / self_x / self_scale / relu: fused epilogue out = act(result + self_scale * self_x + bias)
+        (rof_aggregate_fused); self_x is [num_nodes, dim] indexed by global row id."""
         if tiles == "auto":
             tiles = self.auto_tiles(x.size(1)) if (cache_result is None and phases == 7 and not accumulate) else 1
         if tiles > 1:
             if cache_result is not None or phases != 7 or accumulate:
                 raise RuntimeError("source tiling runs whole passes without a part_result_cache")
             self.launches = 0
-            for k, p in enumerate(self.tile_plans(tiles)):
+            plans = self.tile_plans(tiles)
+            for k, p in enumerate(plans):
+                last = k + 1 == len(plans)                 # the epilogue belongs to the last tile only
                 out = p.aggregate(x, degrees, mode, out=out, workspace=workspace, accumulate=k > 0,
-                                  gather_events=gather_events)
+                                  gather_events=gather_events, bias=bias if last else None,
+                                  self_x=self_x if last else None, self_scale=self_scale, relu=relu and last)
                 self.launches += p.launches
             return out
         if not x.is_cuda:
@@ -248,6 +254,18 @@ class AggregationPlan:
                 raise RuntimeError(f"part_result_cache must be a contiguous float32 CUDA tensor of shape "
                                    f"[{i['num_groups']}, {dim + 1}]")
             cache_ptr = ctypes.c_void_p(cache_result.data_ptr())
+        bias_ptr = self_ptr = None
+        ld_self = 0
+        if bias is not None:
+            if not bias.is_cuda or bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() != dim:
+                raise RuntimeError("bias must be a contiguous float32 CUDA tensor with `dim` entries")
+            bias_ptr = ctypes.c_void_p(bias.data_ptr())
+        if self_x is not None:
+            if (not self_x.is_cuda or self_x.dtype != torch.float32 or self_x.dim() != 2 or self_x.size(1) != dim
+                    or self_x.size(0) != i["num_nodes"] or (self_x.stride(1) != 1 and dim > 1)):
+                raise RuntimeError("self_x must be a float32 CUDA tensor of shape [num_nodes, dim]")
+            self_ptr = ctypes.c_void_p(self_x.data_ptr())
+            ld_self = self_x.stride(0) if self_x.size(0) > 1 else dim
         need = self.workspace_bytes(dim)
         ws = workspace if workspace is not None else (self._get_workspace(need, x.device) if need else None)
         ldx = x.stride(0) if x.size(0) > 1 else dim
@@ -264,11 +282,12 @@ class AggregationPlan:
                 if _NVTX:
                     torch.cuda.nvtx.range_push(_PHASE_NAMES.get(ph, "rof:phases"))
                 try:
-                    _native.check(lib.rof_aggregate_phases(
+                    _native.check(lib.rof_aggregate_fused(
                         self._h, ph | (8 if accumulate else 0), m, ctypes.c_void_p(x.data_ptr()), ldx, dim, deg_ptr,
                         ctypes.c_void_p(out.data_ptr()), ldo, cache_ptr,
                         ctypes.c_void_p(ws.data_ptr()) if ws is not None else None,
-                        ws.numel() if ws is not None else 0, stream))
+                        ws.numel() if ws is not None else 0, bias_ptr, self_ptr, ld_self,
+                        ctypes.c_float(float(self_scale)), int(bool(relu)), stream))
                 finally:
                     if _NVTX:
                         torch.cuda.nvtx.range_pop()

@@ -125,3 +125,26 @@ class ROF_GCNConv(torch.nn.Module):
         inputInfo.dimWorker = self.dimWorker
         out = ROF_GCNConvFunc.apply(x, self.weight, inputInfo, self.add_self_loops, self.kernel_type)
         return out if self.bias is None else out + self.bias
+
+    def forward_fused(self, x, inputInfo, relu=False):
+        """Inference-only forward with the bias add (and optionally the ReLU that follows the layer
+        in upstream's model) fused into the aggregation: act(A_hat (x W) + b) in one pass over the
+        output instead of two or three.  No autograd graph is recorded."""
+        if self.add_self_loops:
+            raise NotImplementedError
+        info = inputInfo
+        n = x.size(0)
+        if self.kernel_type == "GNNA":
+            plan = ROF.plan_for_parts(n, info.column_index, info.part_pointers, info.part2Node)
+        elif self.kernel_type == "ROF_v1":
+            plan = ROF.plan_for_v1(n, info.column_index, info.part_pointers, info.part2Node,
+                                   info.part_cache_flagindex, info.part_pointers_cache, info.column_index_cache)
+        elif self.kernel_type == "ROF_v2":
+            plan = ROF.plan_for_v2(n, info.uniqpart_column_index, info.uniqpart_pointers, info.part2Node_ptr,
+                                   info.part2Node_col)
+        else:
+            raise NotImplementedError
+        with torch.no_grad():
+            tmp = torch.mm(x, self.weight)
+            return plan.aggregate(tmp, info.degrees, "gcn", tiles="auto",
+                                  bias=self.bias.detach() if self.bias is not None else None, relu=relu)

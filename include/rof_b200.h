@@ -176,6 +176,20 @@ int rof_aggregate_phases(const rof_plan* plan, int phases, int mode, const float
                          void* workspace, int64_t workspace_bytes, void* stream);
 
 /*
+ * The same pass with the element-wise work that follows it fused into the store of each output row:
+ *     out[v] = act( aggregate(v) + self_scale * self_x[v] + bias ),  act = max(., 0) when relu != 0.
+ * `bias` ([dim]) and `self_x` ([num_nodes, dim], row stride ld_self, addressed by global row id) may be
+ * NULL.  Covers the bias add that upstream's layer does in a separate pass after the operator
+ * (reuse_conv.py:150), the activation its model applies next (ROF_main.py:181), and GIN's
+ * (1 + eps) * x + sum over neighbours.  With source tiles or pipeline stages give the epilogue to the
+ * LAST stage only (the earlier ones accumulate raw sums).  `phases` as in rof_aggregate_phases().
+ */
+int rof_aggregate_fused(const rof_plan* plan, int phases, int mode, const float* x, int64_t ldx, int dim,
+                        const float* degrees, float* out, int64_t ldo, float* cache_result,
+                        void* workspace, int64_t workspace_bytes, const float* bias, const float* self_x,
+                        int64_t ld_self, float self_scale, int relu, void* stream);
+
+/*
  * The same pass for callers that cannot allocate device memory (no counterpart in upstream,
  * whose wrappers allocate freely with torch): no workspace argument — the scratch is a fixed
  * array of ROF_STATIC_SCRATCH_BYTES inside the library, reserved on every GPU that loads it

@@ -167,3 +167,19 @@ def test_gin_inference_matches_a_dense_fp64_model():
         if i + 1 < len(gin.mlps):
             h = np.maximum(h, 0.0)
     assert_close(got, h, rel=1e-4, abs_=1e-4, what="GIN logits")
+
+
+@pytest.mark.parametrize("kernel_type", ["GNNA", "ROF_v1", "ROF_v2"])
+def test_eval_mode_fused_bias_relu_equals_training_path(kernel_type):
+    g, info = make_info("c1_full_ps2")
+    torch.manual_seed(6)
+    model = ROF_GCN(24, 16, 7, 1, dropout=0.0, add_self_loops=False, reuse_size=info.reuse_size,
+                    kernel_type=kernel_type).to(DEV)
+    with torch.no_grad():
+        for layer in model.layers:
+            layer.bias.normal_()
+    x = torch.randn((g["N"], 24), device=DEV)
+    unfused = model(x, info).detach()                       # autograd path: bias and ReLU as separate passes
+    with torch.no_grad():
+        fused = model(x, info)                              # inference path: fused into the gather's store
+    assert_close(fused.cpu().numpy(), unfused.cpu().numpy(), what="fused bias/ReLU vs separate passes")

@@ -263,3 +263,45 @@ def test_source_tiles_give_the_same_sums(tiles, mode):
     gg["degrees"] = np.maximum(g["degrees"], 1.0)
     assert_close(got, oracle(gg, "v2", x, mode), what=f"{tiles} tiles {mode}")
     assert plan.auto_tiles(40) == 1 and plan.auto_tiles(1 << 20) >= 1
+
+
+@pytest.mark.parametrize("dim", [7, 48, 2052])
+@pytest.mark.parametrize("tiles", [1, 3])
+@pytest.mark.parametrize("mode", ["sum", "gcn"])
+def test_fused_epilogue_equals_separate_elementwise_passes(dim, tiles, mode):
+    """out = relu(aggregate + self_scale * x_self + bias) fused into the store (rof_aggregate_fused)
+    against the plain pass followed by torch element-wise ops; rows split into segments take the
+    epilogue in the segment-reduce kernel, tiled passes only in their last tile"""
+    n = 1200
+    rows = [np.arange(n, dtype=np.int32), np.arange(1, n, 3, dtype=np.int32)] + \
+           [np.unique(np.array([(5 * v) % n, (7 * v + 1) % n, (v * v) % n], dtype=np.int32)) for v in range(2, n)]
+    rows[17] = np.zeros(0, np.int32)                       # an empty row still gets bias and self term
+    ptr = np.concatenate([[0], np.cumsum([len(r) for r in rows])]).astype(np.int32)
+    plan = AggregationPlan.from_parts(n, dev_i32(np.concatenate(rows)), dev_i32(ptr), dev_i32(np.arange(n)))
+    assert plan.info["split_rows"] == 2
+    gen = torch.Generator(device=DEV); gen.manual_seed(dim * 10 + tiles)
+    x = torch.randn((n, dim), device=DEV, generator=gen)
+    xs = torch.randn((n, dim), device=DEV, generator=gen)
+    b = torch.randn((dim,), device=DEV, generator=gen)
+    deg = torch.from_numpy(np.maximum(np.diff(ptr), 1).astype(np.float32)).to(DEV)
+    base = plan.aggregate(x, deg, mode, tiles=tiles)
+    for kw, want in (
+        (dict(bias=b), base + b),
+        (dict(self_x=xs, self_scale=1.5), base + 1.5 * xs),
+        (dict(bias=b, self_x=xs, self_scale=-0.25, relu=True), torch.relu(base - 0.25 * xs + b)),
+        (dict(relu=True), torch.relu(base)),
+    ):
+        got = plan.aggregate(x, deg, mode, tiles=tiles, **kw)
+        assert_close(got.cpu().numpy(), want.cpu().numpy(), what=f"{sorted(kw)} dim {dim} tiles {tiles} {mode}")
+
+
+def test_fused_epilogue_with_reuse_groups():
+    g = load_golden("c5_n1024_ps2")
+    N = g["N"]
+    plan = AggregationPlan.from_v2(N, *[dev_i32(a) for a in layout_args(g["layouts"], "v2")])
+    x = torch.randn((N, 64), device=DEV)
+    b = torch.randn((64,), device=DEV)
+    deg = torch.from_numpy(np.maximum(g["degrees"], 1.0)).to(DEV)
+    want = torch.relu(plan.aggregate(x, deg, "gcn") + 2.0 * x + b)
+    got = plan.aggregate(x, deg, "gcn", bias=b, self_x=x, self_scale=2.0, relu=True)
+    assert_close(got.cpu().numpy(), want.cpu().numpy(), what="fused epilogue, ROF_v2 plan")
