@@ -18,11 +18,14 @@ struct Workspace {
   int64_t total;
 };
 
+// narrow rows run on the plan's finer cut (more, shorter work items)
+inline bool use_fine_cut(const rof_plan* p, int dim) { return p->fine.num_items > 0 && dim <= rof::kNarrowRowFloats; }
+
 Workspace workspace_for(const rof_plan* p, int dim) {
   Workspace w;
   w.ld = scratch_ld(dim);
   w.partial_bytes = round_up((int64_t)p->num_groups * w.ld * 4, 256);
-  w.slot_bytes = round_up((int64_t)p->num_slots * w.ld * 4, 256);
+  w.slot_bytes = round_up((int64_t)(use_fine_cut(p, dim) ? p->fine.num_slots : p->num_slots) * w.ld * 4, 256);
   w.total = w.partial_bytes + w.slot_bytes;
   return w;
 }
@@ -94,7 +97,13 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
     }
   }
   float* partials = p->num_groups ? reinterpret_cast<float*>(workspace) : nullptr;
-  float* slots = p->num_slots ? reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + w.partial_bytes) : nullptr;
+  const bool fine = use_fine_cut(p, dim);
+  const WorkItem* items = fine ? p->fine.d_items : p->d_items;
+  const int num_items = fine ? p->fine.num_items : p->num_items;
+  const SplitRow* split = fine ? p->fine.d_split : p->d_split;
+  const int num_split = fine ? p->fine.num_split_rows : p->num_split_rows;
+  const int num_slots = fine ? p->fine.num_slots : p->num_slots;
+  float* slots = num_slots ? reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + w.partial_bytes) : nullptr;
 
   if (p->device < 0) { set_error("rof_aggregate: the plan was built without a CUDA device and cannot run"); return ROF_ERR_CUDA; }
   int dev = 0;
@@ -118,7 +127,7 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
   }
   if (phases & ROF_PHASE_GATHER) {  // phase B: one pass over every destination row
     GatherArgs a{};
-    a.items = p->d_items; a.num_items = p->num_items; a.col = p->d_col;
+    a.items = items; a.num_items = num_items; a.col = p->d_col;
     a.x = x; a.ldx = ldx; a.partials = partials; a.ldp = w.ld; a.degrees = degrees;
     a.out = out; a.ldo = ldo; a.slots = slots; a.lds = w.ld;
     a.mirror = nullptr; a.ldm = 0; a.mirror_flag_col = -1;
@@ -129,9 +138,9 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
     if (e != cudaSuccess) return cuda_fail(e, "phase B (destination gather)");
     g_last_launches += (dim + 2047) / 2048;
   }
-  if (p->num_split_rows > 0 && (phases & ROF_PHASE_REDUCE)) {
+  if (num_split > 0 && (phases & ROF_PHASE_REDUCE)) {
     ReduceArgs r{};
-    r.rows = p->d_split; r.num_rows = p->num_split_rows; r.slots = slots; r.lds = w.ld; r.degrees = degrees;
+    r.rows = split; r.num_rows = num_split; r.slots = slots; r.lds = w.ld; r.degrees = degrees;
     r.out = out; r.ldo = ldo; r.row_begin = p->row_begin; r.dim = dim; r.scale_mode = scale_mode;
     r.accumulate = accumulate;
     r.ep = ep;

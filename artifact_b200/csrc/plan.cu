@@ -135,41 +135,56 @@ int finalize_plan(HostPlan& hp, rof_plan** out, cudaStream_t stream) {
     return (hp.row_ptr[a + 1] - hp.row_ptr[a]) > (hp.row_ptr[b + 1] - hp.row_ptr[b]);
   });
 
-  std::vector<WorkItem> items;
-  std::vector<SplitRow> split;
   // Segment length.  Long segments are cheaper (fewer segment sums to store and re-read, less
-  // per-item overhead: on the 114.6M-edge graph 8192-entry segments beat 256-entry ones by 18 %),
-  // but a small plan cut into long segments leaves SMs idle at the end (one eighth of that graph:
-  // 0.95 ms with 1024, 1.5 ms with 4096).  Aim at ~16k segments — a few per resident warp of
-  // a B200 (148 SMs x 32 warps) — rounded to a power of two within [256, 8192].
-  int seg = kMinSegmentEdges;
-  while (seg < kMaxSegmentEdges && (double)entries / kTargetSegments > 1.4142 * seg) seg *= 2;
-  p->segment_edges = seg;
-  items.reserve((size_t)rows + (size_t)(entries / seg) + 1);
-  int slots = 0;
-  for (int32_t r : order) {
-    const int64_t b = hp.row_ptr[r], en = hp.row_ptr[r + 1];
-    const int64_t len = en - b;
-    if (len <= seg) {
-      items.push_back(WorkItem{(int32_t)b, (int32_t)en, hp.row_begin + r, (int32_t)row_mid[(size_t)r]});
-    } else {
-      const int nseg = (int)((len + seg - 1) / seg);
-      split.push_back(SplitRow{hp.row_begin + r, slots, nseg, 0});
-      for (int s = 0; s < nseg; ++s) {
-        const int64_t sb = b + (int64_t)s * seg;
-        const int64_t se = std::min(en, sb + seg);
-        const int64_t sm = std::min(se, std::max(sb, row_mid[(size_t)r]));
-        items.push_back(WorkItem{(int32_t)sb, (int32_t)se, -(slots + s) - 1, (int32_t)sm});
+  // per-item overhead: on the 114.6M-edge graph 8192-entry segments beat 256-entry ones by 18 %
+  // at width 256), but too few of them leave SMs idle at the end (one eighth of that graph:
+  // 0.95 ms with 1024, 1.5 ms with 4096).  The sweet spot is a few segments per resident lane
+  // group — ~16k for wide rows (one group per warp on 148 SMs x 32 warps), four times as many
+  // for rows of at most 32 floats (4 or 8 groups per warp: 0.96 ms vs 1.20 ms there) — so the
+  // plan carries two cuts of the same rows and rof_aggregate() picks by feature width.
+  auto segment_length = [&](double target) {
+    int seg = kMinSegmentEdges;
+    while (seg < kMaxSegmentEdges && (double)entries / target > 1.4142 * seg) seg *= 2;
+    return seg;
+  };
+  auto cut = [&](int seg, std::vector<WorkItem>& items, std::vector<SplitRow>& split) {
+    items.clear(); split.clear();
+    items.reserve((size_t)rows + (size_t)(entries / seg) + 1);
+    int slots = 0;
+    for (int32_t r : order) {
+      const int64_t b = hp.row_ptr[r], en = hp.row_ptr[r + 1];
+      const int64_t len = en - b;
+      if (len <= seg) {
+        items.push_back(WorkItem{(int32_t)b, (int32_t)en, hp.row_begin + r, (int32_t)row_mid[(size_t)r]});
+      } else {
+        const int nseg = (int)((len + seg - 1) / seg);
+        split.push_back(SplitRow{hp.row_begin + r, slots, nseg, 0});
+        for (int s = 0; s < nseg; ++s) {
+          const int64_t sb = b + (int64_t)s * seg;
+          const int64_t se = std::min(en, sb + seg);
+          const int64_t sm = std::min(se, std::max(sb, row_mid[(size_t)r]));
+          items.push_back(WorkItem{(int32_t)sb, (int32_t)se, -(slots + s) - 1, (int32_t)sm});
+        }
+        slots += nseg;
       }
-      slots += nseg;
     }
-  }
-  // full segments first, then everything else by length (split rows' short tails included)
-  std::stable_sort(items.begin(), items.end(),
-                   [](const WorkItem& a, const WorkItem& b) { return (a.end - a.begin) > (b.end - b.begin); });
+    // full segments first, then everything else by length (split rows' short tails included)
+    std::stable_sort(items.begin(), items.end(),
+                     [](const WorkItem& a, const WorkItem& b) { return (a.end - a.begin) > (b.end - b.begin); });
+    return slots;
+  };
+  std::vector<WorkItem> items, fine_items;
+  std::vector<SplitRow> split, fine_split;
+  p->segment_edges = segment_length(kTargetSegments);
+  p->num_slots = cut(p->segment_edges, items, split);
   p->num_items = (int)items.size();
   p->num_split_rows = (int)split.size();
-  p->num_slots = slots;
+  p->fine.segment_edges = segment_length(4.0 * kTargetSegments);
+  if (p->fine.segment_edges != p->segment_edges) {
+    p->fine.num_slots = cut(p->fine.segment_edges, fine_items, fine_split);
+    p->fine.num_items = (int)fine_items.size();
+    p->fine.num_split_rows = (int)fine_split.size();
+  }
 
   std::vector<WorkItem> gitems((size_t)p->num_groups);
   for (int g = 0; g < p->num_groups; ++g)
@@ -216,6 +231,8 @@ int finalize_plan(HostPlan& hp, rof_plan** out, cudaStream_t stream) {
   if (rc == ROF_OK) rc = upload((void**)&p->d_items, items.data(), sizeof(WorkItem) * items.size(), "upload work items");
   if (rc == ROF_OK) rc = upload((void**)&p->d_group_items, gitems.data(), sizeof(WorkItem) * gitems.size(), "upload group items");
   if (rc == ROF_OK) rc = upload((void**)&p->d_split, split.data(), sizeof(SplitRow) * split.size(), "upload split rows");
+  if (rc == ROF_OK) rc = upload((void**)&p->fine.d_items, fine_items.data(), sizeof(WorkItem) * fine_items.size(), "upload work items (narrow rows)");
+  if (rc == ROF_OK) rc = upload((void**)&p->fine.d_split, fine_split.data(), sizeof(SplitRow) * fine_split.size(), "upload split rows (narrow rows)");
   if (rc == ROF_OK) {
     e = cudaStreamSynchronize(stream);  // the host vectors die at return
     if (e != cudaSuccess) rc = cuda_fail(e, "plan upload");
@@ -445,6 +462,8 @@ void rof_plan_destroy(rof_plan* p) {
   cudaFree(p->d_items);
   cudaFree(p->d_group_items);
   cudaFree(p->d_split);
+  cudaFree(p->fine.d_items);
+  cudaFree(p->fine.d_split);
   delete p;
 }
 

@@ -30,7 +30,8 @@ struct __align__(16) SplitRow {
 
 constexpr int kMaxSegmentEdges = 8192;   // longest run of entries one work item sums
 constexpr int kMinSegmentEdges = 256;
-constexpr double kTargetSegments = 16000.0;
+constexpr double kTargetSegments = 16000.0;  // for wide rows; four times as many for narrow ones
+constexpr int kNarrowRowFloats = 32;          // rows up to this width use the finer cut
 
 }  // namespace rof
 
@@ -53,6 +54,14 @@ struct rof_plan {
   rof::WorkItem* d_items = nullptr;   // [num_items] phase B, longest first
   rof::WorkItem* d_group_items = nullptr;  // [num_groups] phase A (begin/end index d_col)
   rof::SplitRow* d_split = nullptr;   // [num_split_rows]
+
+  // the same rows cut into shorter segments, used for narrow feature rows (several lane groups
+  // per warp need more work items); absent (num_items == 0) when both cuts coincide
+  struct FineCut {
+    int num_items = 0, num_split_rows = 0, num_slots = 0, segment_edges = 0;
+    rof::WorkItem* d_items = nullptr;
+    rof::SplitRow* d_split = nullptr;
+  } fine;
 
   // host copies kept for rof_plan_export*(): the small arrays always, the entry arrays
   // only when there is no device to read them back from
