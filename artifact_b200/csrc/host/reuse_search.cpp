@@ -22,8 +22,6 @@
 // tests/test_search_cpu.py checks every output array against upstream's own module.
 #include <algorithm>
 #include <cstdint>
-#include <cstdio>
-#include <cstdlib>
 #include <cstring>
 #include <numeric>
 #include <parallel/algorithm>
@@ -233,7 +231,6 @@ rofh_search* rofh_reuse_search(int n, const int64_t* indptr_dst, const int32_t* 
   // ---- get_part_intersect (sizes only; discard_remainder_part = true) ------------------
   Bitmaps bm;
   build_bitmaps(outg, bitmap_budget_bytes, bm);
-  if (std::getenv("ROFH_TRACE")) fprintf(stderr, "[search] bitmaps %.2fs\n", omp_get_wtime() - t0);
   std::vector<int32_t>& nums = S->arr[ROFH_INTERSECTION_NUM];
   nums.assign((size_t)P, 0);
   {
@@ -260,13 +257,11 @@ rofh_search* rofh_reuse_search(int n, const int64_t* indptr_dst, const int32_t* 
       }
       keys[(size_t)p] = Key{((uint64_t)(u32)big << 32) | (h >> 32), (u32)p};
     }
-    if (std::getenv("ROFH_TRACE")) fprintf(stderr, "[search] keys %.2fs\n", omp_get_wtime() - t0);
     __gnu_parallel::sort(keys.begin(), keys.end());
     while (!keys.empty() && keys.back().h == ~0ull &&
            part_ptr[(size_t)keys.back().p + 1] - part_ptr[(size_t)keys.back().p] != ps)
       keys.pop_back();
     const int64_t F = (int64_t)keys.size();
-    if (std::getenv("ROFH_TRACE")) fprintf(stderr, "[search] sorted %.2fs\n", omp_get_wtime() - t0);
     auto same_tuple = [&](u32 a, u32 b) {
       return std::memcmp(indices_src + part_ptr[a], indices_src + part_ptr[b], sizeof(int32_t) * (size_t)ps) == 0;
     };
