@@ -53,6 +53,10 @@ def host():
             lib.rofh_transpose_csr.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p]
             lib.rofh_symmetrize.restype = None
             lib.rofh_symmetrize.argtypes = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+            lib.rofh_set_num_threads.restype = None
+            lib.rofh_set_num_threads.argtypes = [c_int]
+            lib.rofh_max_threads.restype = c_int
+            lib.rofh_max_threads.argtypes = []
             _host = lib
         return _host
 
@@ -119,3 +123,18 @@ class RofError(RuntimeError):
 def check(status):
     if status != 0:
         raise RofError(status, cuda().rof_last_error().decode("utf-8", "replace"))
+
+
+def host_cores():
+    """cores this process may run on (not what OMP_NUM_THREADS says)"""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def use_all_host_cores():
+    """let the host library's OpenMP regions use every core of the process's affinity mask"""
+    n = host_cores()
+    host().rofh_set_num_threads(n)
+    return n

@@ -184,6 +184,11 @@ void rofh_graph_fetch(const rofh_graph* g, int64_t* indptr, int32_t* indices) {
 
 void rofh_graph_free(rofh_graph* g) { delete g; }
 
+// Thread count of every later OpenMP region of this library (launchers such as torchrun export
+// OMP_NUM_THREADS=1, which would make the generators and the search single-threaded).
+void rofh_set_num_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int rofh_max_threads(void) { return omp_get_max_threads(); }
+
 // Transpose a CSR over destinations into a CSR over sources (rows sorted ascending):
 // the second CSR upstream builds from the swapped COO (middle-main.py:187-198).
 void rofh_transpose_csr(int n, const int64_t* indptr, const int32_t* indices, int64_t* t_indptr,

@@ -120,7 +120,8 @@ def cpu_plain(g, dim, mode, seconds_budget, steps=1, warmup=0, threads=0):
     x = rng.standard_normal((n, dim), dtype=np.float32)
     deg = np.maximum(g.degrees_f32(), 1.0)
     out = np.zeros((n, dim), np.float32)
-    cores = threads or rof_oracle.max_threads()
+    from artifact_b200 import _native
+    cores = threads or _native.host_cores()          # all cores of the affinity mask, whatever OMP_NUM_THREADS says
     ip = g.indptr_dst
     # probe ~1% of the edges to size a sample that fits the budget
     r_probe = int(np.searchsorted(ip, max(1, g.num_edges // 100)))
@@ -175,6 +176,8 @@ def prepare_workload(args, rank, world):
     cache_dir = os.environ.get("ROF_CACHE_DIR", "/tmp/rof_b200_cache")
     path = os.path.join(cache_dir, f"{args.workload}_scale{args.scale}_ps{args.part_size}.npz")
     def compute():
+        from artifact_b200 import _native
+        _native.use_all_host_cores()          # torchrun exports OMP_NUM_THREADS=1; only rank 0 computes
         t0 = time.time()
         g = build_graph(args.workload, args.scale)
         tg = time.time() - t0
