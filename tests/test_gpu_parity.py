@@ -305,3 +305,30 @@ def test_fused_epilogue_with_reuse_groups():
     want = torch.relu(plan.aggregate(x, deg, "gcn") + 2.0 * x + b)
     got = plan.aggregate(x, deg, "gcn", bias=b, self_x=x, self_scale=2.0, relu=True)
     assert_close(got.cpu().numpy(), want.cpu().numpy(), what="fused epilogue, ROF_v2 plan")
+
+
+def test_fuzz_kernels_on_random_graphs():
+    """random small graphs (empty rows, dense rows, every part size, groups or none) through the
+    product's search, all three layouts, all three modes, random widths, against the fp64 oracle"""
+    from artifact_b200 import search as rsearch
+    rng = np.random.default_rng(4242)
+    for trial in range(30):
+        n = int(rng.integers(3, 90))
+        p = float(rng.choice([0.05, 0.2, 0.5, 0.85]))
+        ps = int(rng.integers(2, 6))
+        a = rng.random((n, n)) < p
+        rows = [np.flatnonzero(a[v]).astype(np.int32) for v in range(n)]
+        ip = np.concatenate([[0], np.cumsum([len(r) for r in rows])]).astype(np.int64)
+        ix = np.concatenate(rows).astype(np.int32) if ip[-1] else np.zeros(0, np.int32)
+        t_ip, t_ix = graphs.transpose_csr(n, ip, ix)
+        L = rsearch.reuse_search(ip, ix, t_ip, t_ix, ps)
+        dim = int(rng.choice([1, 3, 4, 6, 16, 33, 64, 100]))
+        x = rng.standard_normal((n, dim)).astype(np.float32)
+        degs = np.maximum(np.diff(ip), 1).astype(np.float32)
+        fake = {"layouts": L, "degrees": degs}
+        tx, tdeg = torch.from_numpy(x).to(DEV), torch.from_numpy(degs).to(DEV)
+        for which in ("parts", "v1", "v2"):
+            plan = BUILDERS[which](n, *[dev_i32(arr) for arr in layout_args(L, which)])
+            for mode in ("gcn", "sum", "mean"):
+                got = plan.aggregate(tx, tdeg, mode, tiles=int(rng.integers(1, 4))).cpu().numpy()
+                assert_close(got, oracle(fake, which, x, mode), what=f"trial {trial} n={n} ps={ps} {which} {mode} D={dim}")

@@ -157,3 +157,42 @@ def test_segment_length_follows_plan_size():
     plan = AggregationPlan.from_parts(n, col, np.array([0, 300, 600, 900], np.int32), np.array([0, 1, 2], np.int32))
     assert plan.info["segment_edges"] == 256            # small plan: shortest segments
     assert plan.info["split_rows"] == 3 and plan.info["num_slots"] == 6
+
+
+def test_fuzz_plans_and_oracle_on_random_graphs():
+    """random small graphs through the product's search, then: every layout's plan expands back to the
+    CSR, staged plans partition it, and the oracle gives the same sums over all three layouts"""
+    import rof_oracle
+    from artifact_b200 import graphs, search
+    rng = np.random.default_rng(77)
+    for trial in range(40):
+        n = int(rng.integers(5, 80))
+        p = float(rng.choice([0.05, 0.2, 0.5, 0.85]))
+        ps = int(rng.integers(2, 6))
+        a = rng.random((n, n)) < p
+        rows = [np.flatnonzero(a[v]).astype(np.int32) for v in range(n)]
+        ip = np.concatenate([[0], np.cumsum([len(r) for r in rows])]).astype(np.int64)
+        ix = np.concatenate(rows).astype(np.int32) if ip[-1] else np.zeros(0, np.int32)
+        t_ip, t_ix = graphs.transpose_csr(n, ip, ix)
+        L = search.reuse_search(ip, ix, t_ip, t_ix, ps)
+        want = [list(r) for r in rows]
+        for which in ("parts", "v1", "v2"):
+            plan = BUILDERS[which](n, *layout_args(L, which))
+            assert expand_rows(plan.export(), n) == want, (trial, which)
+        whole = AggregationPlan.from_v2(n, *layout_args(L, "v2"))
+        tiles = int(rng.integers(2, 5))
+        blk = (n + tiles - 1) // tiles
+        got = [[] for _ in range(n)]
+        for sp in whole.stages(blk, list(range(tiles))):
+            for v, r in enumerate(expand_rows(sp.export(), n)):
+                got[v] += r
+        assert [sorted(r) for r in got] == want
+        x = rng.standard_normal((n, 3)).astype(np.float32)
+        deg = np.maximum(np.diff(ip), 1).astype(np.float32)
+        base = rof_oracle.aggregate_parts(x, L["original_column_index"], deg, L["part_pointers"], L["part2Node"], "gcn", True)
+        cache = np.zeros((len(L["part_pointers_cache"]) - 1, 4), np.float32)
+        v1 = rof_oracle.aggregate_v1(x, L["column_index"], deg, L["part_pointers"], L["part2Node"], cache,
+                                     L["part_cache_flagindex"], L["part_pointers_cache"], L["column_index_cache"], "gcn", True)
+        v2 = rof_oracle.aggregate_v2(x, L["uniqpart_column_index"], deg, L["uniqpart_pointers"], L["part2Node_ptr"],
+                                     L["part2Node_col"], "gcn", True)
+        assert np.allclose(v1, base, rtol=1e-6, atol=1e-6) and np.allclose(v2, base, rtol=1e-6, atol=1e-6)

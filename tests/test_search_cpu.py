@@ -73,3 +73,39 @@ def test_cached_search_round_trips(tmp_path):
     g2 = graphs.config5(4096 / 1048576)                    # another graph: another cache entry
     _, hit_c = search.cached_search_graph(g2, 2, str(tmp_path))
     assert not hit_c and len(list(tmp_path.glob("reuse_*_ps2.npz"))) == 2
+
+
+def _random_graph(rng, n, p):
+    a = rng.random((n, n)) < p
+    ip = np.zeros(n + 1, np.int64)
+    idx = []
+    for v in range(n):
+        r = np.flatnonzero(a[v]).astype(np.int32)
+        idx.append(r)
+        ip[v + 1] = ip[v] + len(r)
+    ix = np.concatenate(idx) if idx else np.zeros(0, np.int32)
+    t_ip, t_ix = graphs.transpose_csr(n, ip, ix.astype(np.int32))
+    return ip, ix.astype(np.int32), t_ip, t_ix
+
+
+def test_fuzz_small_graphs_against_live_upstream():
+    """many small random graphs (dense ones make long tie runs in the fan-out sort, sparse ones empty
+    rows and zero groups), every part size: all 14 arrays equal upstream's"""
+    mod = ref_search.load_module()
+    if mod is None:
+        pytest.skip("upstream preprocessor not built here (oracle/_ref)")
+    rng = np.random.default_rng(2024)
+    checked = groups = 0
+    for trial in range(150):
+        n = int(rng.integers(10, 70))
+        p = float(rng.choice([0.03, 0.1, 0.3, 0.6, 0.9]))
+        ps = int(rng.integers(1, 6))
+        ip, ix, t_ip, t_ix = _random_graph(rng, n, p)
+        if len(ix) == 0:
+            continue
+        ref = ref_search.run(ip, ix, t_ip, t_ix, ps, mod)
+        mine = search.reuse_search(ip, ix, t_ip, t_ix, ps, num_threads=int(rng.integers(1, 4)))
+        compare(mine, ref)
+        checked += 1
+        groups += len(ref["index_picked"])
+    assert checked > 120 and groups > 200
