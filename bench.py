@@ -11,8 +11,10 @@ seeded synthetic graph of the workload, through the reuse plan built from the RO
 `value` is edges/s with the ORIGINAL edge count (reuse shows up as more edges per second),
 inputs resident in HBM; `e2e` is the same step through the public API with pinned-host inputs
 and outputs, copies inside the timed region.  With N > 1 the destination rows are cut into N
-equal blocks, every pass first all-gathers the feature blocks over NCCL, and the same total
-work is divided (strong scaling).  Prints ONE JSON line on rank 0.
+equal blocks; every pass moves the feature blocks between the ranks over NCCL (staged
+send/receive groups overlapped with the per-stage aggregation, or one all-gather with
+--no-pipeline) and the same total work is divided (strong scaling).  On one GPU a feature matrix
+larger than L2 is walked in source tiles (--tiles).  Prints ONE JSON line on rank 0.
 """
 import argparse
 import json
