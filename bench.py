@@ -539,7 +539,7 @@ def main():
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu:
-            cb = cpu_plain(g, D, mode, seconds_budget=20.0)
+            cb = cpu_plain(g, D, mode, seconds_budget=20.0, steps=3, warmup=1)
             cpu = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
         line = {
             "metric": "aggregation edges/s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
