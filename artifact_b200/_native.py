@@ -64,7 +64,8 @@ def host():
 class PlanInfo(ctypes.Structure):
     _fields_ = [(n, c_int64) for n in (
         "num_nodes", "row_begin", "row_end", "num_groups", "group_sources", "gather_entries",
-        "partial_entries", "original_edges", "num_items", "split_rows", "num_slots", "segment_edges")]
+        "partial_entries", "original_edges", "num_items", "split_rows", "num_slots", "segment_edges",
+        "num_tiles", "tile_items", "tile_entries", "tile_shared_entries", "tile_staged_rows")]
 
 
 # every symbol include/rof_b200.h declares: (name, restype, argtypes)
@@ -79,6 +80,7 @@ CUDA_ABI = [
     ("rof_plan_destroy", None, [c_void_p]),
     ("rof_plan_get_info", c_int, [c_void_p, ctypes.POINTER(PlanInfo)]),
     ("rof_plan_export", c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    ("rof_plan_export_tiles", c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     ("rof_plan_workspace_bytes", c_int64, [c_void_p, c_int]),
     ("rof_plan_algorithmic_bytes", c_int64, [c_void_p, c_int, c_int]),
     ("rof_aggregate", c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64, c_void_p,
@@ -90,6 +92,9 @@ CUDA_ABI = [
                                     c_void_p]),
     ("rof_aggregate_static_scratch", c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_void_p, c_void_p, c_int64,
                                              c_void_p]),
+    ("rof_scale_rows", c_int, [c_void_p, c_int64, c_int, c_void_p, c_int, c_void_p, c_int64, c_int64, c_void_p]),
+    ("rof_probe_read", c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
+    ("rof_plan_take_status", c_int, [c_void_p]),
     ("rof_last_launch_count", c_int, []),
     ("rof_last_error", c_char_p, []),
     ("rof_version", c_int, []),

@@ -1,4 +1,7 @@
 // The per-call entry points of the C ABI: argument checks, workspace carving, launches.
+#include <algorithm>
+#include <cstdlib>
+
 #include "rof_internal.h"
 
 namespace {
@@ -19,6 +22,24 @@ struct Workspace {
 };
 
 // narrow rows run on the plan's finer cut (more, shorter work items)
+// ROF_FUSE_REDUCE=0: always combine the segment sums of split rows with a separate launch
+inline bool fuse_reduce_enabled() {
+  static const bool v = [] {
+    const char* e = std::getenv("ROF_FUSE_REDUCE");
+    return e == nullptr || std::string(e) != "0";
+  }();
+  return v;
+}
+
+// Host policy for the gather kernels (see kernels.cu): plans whose work items are short run the
+// pipelined warp-per-item kernel, everything else the lane-group kernel.  The shared-memory ring
+// kernel measured about half as fast as either on B200 (one bulk copy per row of at most a few
+// KB does not keep the copy engine busy) and is only used on request (ROF_KERNEL=ring).
+inline int kernel_for(int num_items, int64_t entries) {
+  if (num_items <= 0) return 0;
+  return ((double)entries / num_items < rof::kShortItemEntries) ? 2 : 0;
+}
+
 inline bool use_fine_cut(const rof_plan* p, int dim) { return p->fine.num_items > 0 && dim <= rof::kNarrowRowFloats; }
 
 Workspace workspace_for(const rof_plan* p, int dim) {
@@ -52,6 +73,7 @@ int64_t rof_plan_algorithmic_bytes(const rof_plan* p, int dim, int mode) {
   // phase A: group sources in, one partial row out, indices, pointers
   if (p->num_groups > 0) b += row_bytes * (p->group_sources + p->num_groups) + 4 * p->group_sources + 4 * ((int64_t)p->num_groups + 1);
   if (mode == ROF_MODE_GCN) b += 4 * (p->gather_entries - p->partial_entries + p->group_sources);  // degree reads
+  if (mode == ROF_MODE_GCN_PRESCALED) b += 4 * rows_out;
   if (mode == ROF_MODE_MEAN) b += 4 * rows_out;
   return b;
 }
@@ -81,7 +103,7 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
   const int accumulate = (phases & ROF_PHASE_ACCUMULATE) ? 1 : 0;
   cudaStream_t stream = (cudaStream_t)stream_;
   if (p == nullptr) { set_error("rof_aggregate: null plan"); return ROF_ERR_BAD_ARGUMENT; }
-  if (mode != ROF_MODE_GCN && mode != ROF_MODE_SUM && mode != ROF_MODE_MEAN) { set_error("rof_aggregate: unknown mode"); return ROF_ERR_BAD_ARGUMENT; }
+  if (mode != ROF_MODE_GCN && mode != ROF_MODE_SUM && mode != ROF_MODE_MEAN && mode != ROF_MODE_GCN_PRESCALED) { set_error("rof_aggregate: unknown mode"); return ROF_ERR_BAD_ARGUMENT; }
   if (dim < 0 || ldx < dim || ldo < dim) { set_error("rof_aggregate: dim/ldx/ldo out of order"); return ROF_ERR_BAD_ARGUMENT; }
   const int rows_out = p->row_end - p->row_begin;
   if (rows_out == 0 || dim == 0) return ROF_OK;
@@ -104,15 +126,23 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
   const int num_split = fine ? p->fine.num_split_rows : p->num_split_rows;
   const int num_slots = fine ? p->fine.num_slots : p->num_slots;
   float* slots = num_slots ? reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + w.partial_bytes) : nullptr;
+  const int32_t* slot_owner = fine ? p->fine.d_slot_owner : p->d_slot_owner;
+  int32_t* arrive = fine ? p->fine.d_arrive : p->d_arrive;
 
   if (p->device < 0) { set_error("rof_aggregate: the plan was built without a CUDA device and cannot run"); return ROF_ERR_CUDA; }
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return cuda_fail(e, "cudaGetDevice");
   if (dev != p->device) { set_error("rof_aggregate: plan was built on another device"); return ROF_ERR_BAD_ARGUMENT; }
+  if (p->h_status != nullptr && *reinterpret_cast<volatile int*>(p->h_status) != 0) {
+    *p->h_status = 0;
+    set_error("rof_aggregate: a bounded wait inside an earlier pass on this plan ran out; that pass's output is incomplete");
+    return ROF_ERR_WAIT_LIMIT;
+  }
 
   const int gcn = (mode == ROF_MODE_GCN);
-  const int scale_mode = gcn ? 1 : (mode == ROF_MODE_MEAN ? 2 : 0);
+  const int scale_mode = (gcn || mode == ROF_MODE_GCN_PRESCALED) ? 1 : (mode == ROF_MODE_MEAN ? 2 : 0);
+  bool reduce_done = false;
 
   if (p->num_groups > 0 && (phases & ROF_PHASE_PARTIALS)) {  // phase A: one partial row per reuse group
     GatherArgs a{};
@@ -121,9 +151,9 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
     a.out = partials; a.ldo = w.ld; a.slots = nullptr; a.lds = 0;
     a.mirror = cache_result; a.ldm = (int64_t)dim + 1; a.mirror_flag_col = cache_result ? dim : -1;
     a.num_nodes = p->num_nodes; a.row_begin = 0; a.dim = dim; a.weight_gcn = gcn; a.scale_mode = 0;
-    e = launch_gather(a, stream);
+    a.out_padded = 1; a.kernel = kernel_for(p->num_groups, p->group_sources); a.status = p->d_status;
+    e = launch_gather(a, stream, &g_last_launches);
     if (e != cudaSuccess) return cuda_fail(e, "phase A (group partial sums)");
-    g_last_launches += (dim + 2047) / 2048;
   }
   if (phases & ROF_PHASE_GATHER) {  // phase B: one pass over every destination row
     GatherArgs a{};
@@ -134,11 +164,28 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
     a.num_nodes = p->num_nodes; a.row_begin = p->row_begin; a.dim = dim; a.weight_gcn = gcn; a.scale_mode = scale_mode;
     a.accumulate = accumulate;
     a.ep = ep;
-    e = launch_gather(a, stream);
+    a.kernel = kernel_for(num_items, p->gather_entries); a.status = p->d_status;
+    // short rows that share entries: staged once per tile in shared memory; the other items
+    // (long rows, segments of split rows) follow with the lane-group kernel
+    const bool tiled = p->tiled.num_tiles > 0 && tiles_supported(a);
+    if (tiled) {
+      TileArgs t{p->tiled.d_tiles, p->tiled.d_titems, p->tiled.d_tcol, p->tiled.d_stage_col, p->tiled.num_tiles};
+      e = launch_gather_tiles(a, t, stream, &g_last_launches);
+      if (e != cudaSuccess) return cuda_fail(e, "phase B (shared-memory tiles)");
+      a.items = fine ? p->tiled.d_rest_items_fine : p->tiled.d_rest_items;
+      a.num_items = fine ? p->tiled.num_rest_fine : p->tiled.num_rest;
+      a.kernel = 0;
+    }
+    // when the caller wants the whole pass, the last segment of a split row to arrive finishes it
+    if (num_split > 0 && (phases & ROF_PHASE_REDUCE) && fuse_reduce_enabled()) {
+      a.slot_owner = slot_owner; a.split = split; a.arrive = arrive;
+      reduce_done = gather_fuses_reduce(a);
+      if (!reduce_done) a.arrive = nullptr;
+    }
+    e = launch_gather(a, stream, &g_last_launches);
     if (e != cudaSuccess) return cuda_fail(e, "phase B (destination gather)");
-    g_last_launches += (dim + 2047) / 2048;
   }
-  if (num_split > 0 && (phases & ROF_PHASE_REDUCE)) {
+  if (num_split > 0 && (phases & ROF_PHASE_REDUCE) && !reduce_done) {
     ReduceArgs r{};
     r.rows = split; r.num_rows = num_split; r.slots = slots; r.lds = w.ld; r.degrees = degrees;
     r.out = out; r.ldo = ldo; r.row_begin = p->row_begin; r.dim = dim; r.scale_mode = scale_mode;
@@ -149,6 +196,39 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
     g_last_launches += 1;
   }
   return ROF_OK;
+}
+
+int rof_scale_rows(const float* x, int64_t ldx, int dim, const float* degrees, int op, float* out, int64_t ldo,
+                   int64_t num_rows, void* stream_) {
+  if (num_rows < 0 || num_rows > 0x7fffffffLL || dim < 0 || ldx < dim || ldo < dim || op < 0 || op > 2) {
+    set_error("rof_scale_rows: sizes out of order or unknown op");
+    return ROF_ERR_BAD_ARGUMENT;
+  }
+  if (num_rows == 0 || dim == 0) return ROF_OK;
+  if (x == nullptr || out == nullptr || (op != ROF_SCALE_COPY && degrees == nullptr)) {
+    set_error("rof_scale_rows: null pointer");
+    return ROF_ERR_BAD_ARGUMENT;
+  }
+  // the padding columns up to the next multiple of 4 floats are zeroed when the row has room for them
+  const int pad_to = (int)std::min<int64_t>(round_up(dim, 4), ldo);
+  const cudaError_t e = launch_scale_rows(x, ldx, degrees, out, ldo, (int)num_rows, dim, pad_to, op, (cudaStream_t)stream_);
+  return e == cudaSuccess ? ROF_OK : cuda_fail(e, "rof_scale_rows");
+}
+
+int rof_probe_read(const void* buffer, int64_t bytes, int repeats, float* sink, void* stream_) {
+  if (buffer == nullptr || sink == nullptr || bytes < 0 || repeats < 0 || (reinterpret_cast<uintptr_t>(buffer) & 15)) {
+    set_error("rof_probe_read: null or misaligned buffer");
+    return ROF_ERR_BAD_ARGUMENT;
+  }
+  const cudaError_t e = launch_probe_read(buffer, bytes, repeats, sink, (cudaStream_t)stream_);
+  return e == cudaSuccess ? ROF_OK : cuda_fail(e, "rof_probe_read");
+}
+
+int rof_plan_take_status(rof_plan* p) {
+  if (p == nullptr || p->h_status == nullptr) return 0;
+  const int v = *reinterpret_cast<volatile int*>(p->h_status);
+  *p->h_status = 0;
+  return v;
 }
 
 int rof_last_launch_count(void) { return g_last_launches; }

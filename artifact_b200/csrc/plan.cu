@@ -9,6 +9,7 @@
 // fixed order, so the result is deterministic.  Work items are ordered longest first so the
 // hardware block scheduler balances the power-law tail.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <numeric>
@@ -90,9 +91,150 @@ int sync_if_device(int where, cudaStream_t stream) {
 }  // namespace
 
 // ---------------------------------------------------------------------------------------
+// shared-memory tiles
+// ---------------------------------------------------------------------------------------
+namespace {
+
+struct HostTiles {
+  std::vector<int32_t> tcol, stage_col;
+  std::vector<WorkItem> titems;
+  std::vector<TileDesc> tiles;
+  int64_t entries = 0, shared_entries = 0, staged_rows = 0;
+};
+
+// The ids that occur at least twice among `ents`, most frequent first (ties: smaller id first),
+// at most kTileMaxStage of them.  `sorted` is scratch.  Returns how many global row reads staging
+// them saves: sum over kept ids of (occurrences - 1).
+int64_t shared_ids_of_tile(const std::vector<int32_t>& ents, std::vector<int32_t>& sorted,
+                           std::vector<std::pair<int32_t, int32_t>>& kept) {
+  sorted = ents;
+  std::sort(sorted.begin(), sorted.end());
+  kept.clear();
+  for (size_t i = 0; i < sorted.size();) {
+    size_t j = i + 1;
+    while (j < sorted.size() && sorted[j] == sorted[i]) ++j;
+    if (j - i >= 2) kept.emplace_back((int32_t)(j - i), sorted[i]);   // (count, id)
+    i = j;
+  }
+  std::sort(kept.begin(), kept.end(), [](const std::pair<int32_t, int32_t>& a, const std::pair<int32_t, int32_t>& b) {
+    return a.first != b.first ? a.first > b.first : a.second < b.second;
+  });
+  if ((int)kept.size() > kTileMaxStage) kept.resize(kTileMaxStage);
+  int64_t saved = 0;
+  for (const auto& k : kept) saved += k.first - 1;
+  return saved;
+}
+
+// ROF_TILES=0 never builds tiles, ROF_TILES=1 always does (when there are eligible rows); unset:
+// tiles are built when a sample of them saves at least kTileMinSaved of the global row reads.
+int tiles_override() {
+  const char* e = std::getenv("ROF_TILES");
+  if (e == nullptr || e[0] == '\0') return -1;
+  return e[0] == '0' ? 0 : 1;
+}
+
+// Groups the short rows of `hp`, in row order, into tiles and rewrites their entries.  Returns
+// false (and leaves `out` empty) when tiling does not pay.
+bool build_tiles(const HostPlan& hp, HostTiles& out) {
+  const int rows = hp.row_end - hp.row_begin;
+  const int ov = tiles_override();
+  if (ov == 0 || rows == 0) return false;
+  std::vector<int32_t> elig;
+  elig.reserve((size_t)rows);
+  int64_t elig_entries = 0;
+  for (int r = 0; r < rows; ++r) {
+    const int64_t len = hp.row_ptr[r + 1] - hp.row_ptr[r];
+    if (len <= kTileMaxRowEntries) { elig.push_back(r); elig_entries += len; }
+  }
+  if (elig.empty() || elig_entries == 0) return false;
+  const int num_tiles = (int)((elig.size() + kTileRows - 1) / kTileRows);
+  auto tile_entries = [&](int t, std::vector<int32_t>& ents) {
+    ents.clear();
+    const size_t e0 = (size_t)t * kTileRows, e1 = std::min(elig.size(), e0 + kTileRows);
+    for (size_t k = e0; k < e1; ++k) {
+      const int r = elig[k];
+      ents.insert(ents.end(), hp.col.begin() + hp.row_ptr[r], hp.col.begin() + hp.row_ptr[r + 1]);
+    }
+  };
+  if (ov < 0) {   // sample up to 256 tiles, evenly spread
+    std::vector<int32_t> ents, sorted;
+    std::vector<std::pair<int32_t, int32_t>> kept;
+    const int step = std::max(1, num_tiles / 256);
+    int64_t saved = 0, total = 0;
+    for (int t = 0; t < num_tiles; t += step) {
+      tile_entries(t, ents);
+      saved += shared_ids_of_tile(ents, sorted, kept);
+      total += (int64_t)ents.size();
+    }
+    if (total == 0 || (double)saved < kTileMinSaved * (double)total) return false;
+  }
+
+  std::vector<int64_t> tptr(elig.size() + 1, 0);   // entry offsets of the tiled rows
+  for (size_t k = 0; k < elig.size(); ++k) tptr[k + 1] = tptr[k] + (hp.row_ptr[elig[k] + 1] - hp.row_ptr[elig[k]]);
+  out.entries = elig_entries;
+  out.tcol.resize((size_t)elig_entries);
+  out.titems.resize(elig.size());
+  out.tiles.resize((size_t)num_tiles);
+  out.stage_col.assign((size_t)num_tiles * kTileMaxStage, 0);
+  int64_t shared_total = 0, staged_total = 0;
+#pragma omp parallel reduction(+ : shared_total, staged_total)
+  {
+    std::vector<int32_t> ents, sorted;
+    std::vector<std::pair<int32_t, int32_t>> kept, by_id;
+#pragma omp for schedule(dynamic, 64)
+    for (int t = 0; t < num_tiles; ++t) {
+      tile_entries(t, ents);
+      shared_ids_of_tile(ents, sorted, kept);
+      by_id.clear();
+      for (int sidx = 0; sidx < (int)kept.size(); ++sidx) {
+        out.stage_col[(size_t)t * kTileMaxStage + sidx] = kept[sidx].second;
+        by_id.emplace_back(kept[sidx].second, sidx);   // (id, slot)
+      }
+      std::sort(by_id.begin(), by_id.end());
+      auto slot_of = [&](int32_t c) {
+        auto it = std::lower_bound(by_id.begin(), by_id.end(), std::make_pair(c, (int32_t)-1));
+        return (it != by_id.end() && it->first == c) ? it->second : -1;
+      };
+      const size_t e0 = (size_t)t * kTileRows, e1 = std::min(elig.size(), e0 + kTileRows);
+      out.tiles[(size_t)t] = TileDesc{(int32_t)e0, (int32_t)(e1 - e0), (int32_t)(t * kTileMaxStage), (int32_t)kept.size()};
+      staged_total += (int64_t)kept.size();
+      for (size_t k = e0; k < e1; ++k) {
+        const int r = elig[k];
+        int64_t w = tptr[k];
+        for (int64_t q = hp.row_ptr[r]; q < hp.row_ptr[r + 1]; ++q) {   // staged slots first ...
+          const int sl = slot_of(hp.col[(size_t)q]);
+          if (sl >= 0) out.tcol[(size_t)w++] = sl;
+        }
+        const int64_t mid = w;
+        for (int64_t q = hp.row_ptr[r]; q < hp.row_ptr[r + 1]; ++q)     // ... then the rows read from global memory
+          if (slot_of(hp.col[(size_t)q]) < 0) out.tcol[(size_t)w++] = hp.col[(size_t)q];
+        shared_total += mid - tptr[k];
+        out.titems[k] = WorkItem{(int32_t)tptr[k], (int32_t)tptr[k + 1], hp.row_begin + r, (int32_t)mid};
+      }
+    }
+  }
+  out.shared_entries = shared_total;
+  out.staged_rows = staged_total;
+  return true;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------
 // finalize: row lists -> sorted work items -> device
 // ---------------------------------------------------------------------------------------
+static int finalize_plan_impl(HostPlan& hp, rof_plan** out, cudaStream_t stream);
+
 int finalize_plan(HostPlan& hp, rof_plan** out, cudaStream_t stream) {
+  try {
+    return finalize_plan_impl(hp, out, stream);
+  } catch (const std::bad_alloc&) {  // never let an exception cross the C ABI
+    set_error("out of host memory while building the plan");
+    return ROF_ERR_NO_MEMORY;
+  }
+}
+
+static int finalize_plan_impl(HostPlan& hp, rof_plan** out, cudaStream_t stream) {
   const int rows = hp.row_end - hp.row_begin;
   const int64_t entries = (int64_t)hp.col.size();
   const int64_t gsrc = (int64_t)hp.group_col.size();
@@ -191,6 +333,30 @@ int finalize_plan(HostPlan& hp, rof_plan** out, cudaStream_t stream) {
     gitems[g] = WorkItem{(int32_t)(entries + hp.group_ptr[g]), (int32_t)(entries + hp.group_ptr[g + 1]), g,
                          (int32_t)(entries + hp.group_ptr[g])};
 
+  // shared-memory tiles for the short rows, and the items each cut keeps for the lane-group kernel
+  HostTiles ht;
+  std::vector<WorkItem> rest, rest_fine;
+  if (build_tiles(hp, ht)) {
+    auto keep_rest = [](const std::vector<WorkItem>& all, std::vector<WorkItem>& out_items) {
+      out_items.clear();
+      for (const WorkItem& w : all)
+        if (w.dst < 0 || w.end - w.begin > kTileMaxRowEntries) out_items.push_back(w);
+    };
+    keep_rest(items, rest);
+    keep_rest(fine_items, rest_fine);
+    p->tiled.num_tiles = (int)ht.tiles.size();
+    p->tiled.num_items = (int)ht.titems.size();
+    p->tiled.entries = ht.entries;
+    p->tiled.shared_entries = ht.shared_entries;
+    p->tiled.staged_rows = ht.staged_rows;
+    p->tiled.num_rest = (int)rest.size();
+    p->tiled.num_rest_fine = (int)rest_fine.size();
+    p->tiled.h_tiles = ht.tiles;
+    p->tiled.h_titems = ht.titems;
+    p->tiled.h_tcol = ht.tcol;
+    p->tiled.h_stage_col = ht.stage_col;
+  }
+
   p->h_row_ptr = hp.row_ptr;
   p->h_group_ptr = hp.group_ptr;
   p->h_items = items;
@@ -233,6 +399,42 @@ int finalize_plan(HostPlan& hp, rof_plan** out, cudaStream_t stream) {
   if (rc == ROF_OK) rc = upload((void**)&p->d_split, split.data(), sizeof(SplitRow) * split.size(), "upload split rows");
   if (rc == ROF_OK) rc = upload((void**)&p->fine.d_items, fine_items.data(), sizeof(WorkItem) * fine_items.size(), "upload work items (narrow rows)");
   if (rc == ROF_OK) rc = upload((void**)&p->fine.d_split, fine_split.data(), sizeof(SplitRow) * fine_split.size(), "upload split rows (narrow rows)");
+  // which split row every scratch slot belongs to, and the rows' arrival counters (zero between passes)
+  auto owners_of = [](const std::vector<SplitRow>& sp, int slots) {
+    std::vector<int32_t> o((size_t)slots);
+    for (size_t i = 0; i < sp.size(); ++i)
+      for (int k = 0; k < sp[i].count; ++k) o[(size_t)sp[i].first_slot + k] = (int32_t)i;
+    return o;
+  };
+  auto counters = [&](int32_t** dptr, size_t n) -> int {
+    *dptr = nullptr;
+    if (n == 0) return ROF_OK;
+    cudaError_t err = cudaMalloc((void**)dptr, sizeof(int32_t) * n);
+    if (err != cudaSuccess) return cuda_fail(err, "cudaMalloc(arrival counters)");
+    err = cudaMemsetAsync(*dptr, 0, sizeof(int32_t) * n, stream);
+    return err == cudaSuccess ? ROF_OK : cuda_fail(err, "clear arrival counters");
+  };
+  const std::vector<int32_t> owners = owners_of(split, p->num_slots), fine_owners = owners_of(fine_split, p->fine.num_slots);
+  if (rc == ROF_OK) rc = upload((void**)&p->d_slot_owner, owners.data(), sizeof(int32_t) * owners.size(), "upload slot owners");
+  if (rc == ROF_OK) rc = upload((void**)&p->fine.d_slot_owner, fine_owners.data(), sizeof(int32_t) * fine_owners.size(), "upload slot owners (narrow rows)");
+  if (p->tiled.num_tiles > 0) {
+    if (rc == ROF_OK) rc = upload((void**)&p->tiled.d_tcol, ht.tcol.data(), sizeof(int32_t) * ht.tcol.size(), "upload tile entries");
+    if (rc == ROF_OK) rc = upload((void**)&p->tiled.d_titems, ht.titems.data(), sizeof(WorkItem) * ht.titems.size(), "upload tile items");
+    if (rc == ROF_OK) rc = upload((void**)&p->tiled.d_tiles, ht.tiles.data(), sizeof(TileDesc) * ht.tiles.size(), "upload tiles");
+    if (rc == ROF_OK) rc = upload((void**)&p->tiled.d_stage_col, ht.stage_col.data(), sizeof(int32_t) * ht.stage_col.size(), "upload tile stage lists");
+    if (rc == ROF_OK) rc = upload((void**)&p->tiled.d_rest_items, rest.data(), sizeof(WorkItem) * rest.size(), "upload untiled items");
+    if (rc == ROF_OK) rc = upload((void**)&p->tiled.d_rest_items_fine, rest_fine.data(), sizeof(WorkItem) * rest_fine.size(), "upload untiled items (narrow rows)");
+  }
+  if (rc == ROF_OK) rc = counters(&p->d_arrive, split.size());
+  if (rc == ROF_OK) rc = counters(&p->fine.d_arrive, fine_split.size());
+  if (rc == ROF_OK) {
+    e = cudaHostAlloc((void**)&p->h_status, sizeof(int), cudaHostAllocMapped);
+    if (e == cudaSuccess) {
+      *p->h_status = 0;
+      e = cudaHostGetDevicePointer((void**)&p->d_status, p->h_status, 0);
+    }
+    if (e != cudaSuccess) rc = cuda_fail(e, "status word");
+  }
   if (rc == ROF_OK) {
     e = cudaStreamSynchronize(stream);  // the host vectors die at return
     if (e != cudaSuccess) rc = cuda_fail(e, "plan upload");
@@ -456,6 +658,16 @@ int rof_plan_export(const rof_plan* p, int64_t* row_ptr, int32_t* col, int32_t* 
   return e == cudaSuccess ? ROF_OK : cuda_fail(e, "rof_plan_export");
 }
 
+int rof_plan_export_tiles(const rof_plan* p, int32_t* tiles, int32_t* titems, int32_t* tcol, int32_t* stage_col) {
+  if (p == nullptr) { set_error("rof_plan_export_tiles: null plan"); return ROF_ERR_BAD_ARGUMENT; }
+  const auto& t = p->tiled;
+  if (tiles) std::memcpy(tiles, t.h_tiles.data(), sizeof(TileDesc) * t.h_tiles.size());
+  if (titems) std::memcpy(titems, t.h_titems.data(), sizeof(WorkItem) * t.h_titems.size());
+  if (tcol) std::memcpy(tcol, t.h_tcol.data(), sizeof(int32_t) * t.h_tcol.size());
+  if (stage_col) std::memcpy(stage_col, t.h_stage_col.data(), sizeof(int32_t) * t.h_stage_col.size());
+  return ROF_OK;
+}
+
 void rof_plan_destroy(rof_plan* p) {
   if (p == nullptr) return;
   cudaFree(p->d_col);
@@ -464,6 +676,17 @@ void rof_plan_destroy(rof_plan* p) {
   cudaFree(p->d_split);
   cudaFree(p->fine.d_items);
   cudaFree(p->fine.d_split);
+  cudaFree(p->tiled.d_tcol);
+  cudaFree(p->tiled.d_titems);
+  cudaFree(p->tiled.d_tiles);
+  cudaFree(p->tiled.d_stage_col);
+  cudaFree(p->tiled.d_rest_items);
+  cudaFree(p->tiled.d_rest_items_fine);
+  cudaFree(p->d_slot_owner);
+  cudaFree(p->d_arrive);
+  cudaFree(p->fine.d_slot_owner);
+  cudaFree(p->fine.d_arrive);
+  if (p->h_status) cudaFreeHost(p->h_status);
   delete p;
 }
 
@@ -481,6 +704,11 @@ int rof_plan_get_info(const rof_plan* p, rof_plan_info* info) {
   info->split_rows = p->num_split_rows;
   info->num_slots = p->num_slots;
   info->segment_edges = p->segment_edges;
+  info->num_tiles = p->tiled.num_tiles;
+  info->tile_items = p->tiled.num_items;
+  info->tile_entries = p->tiled.entries;
+  info->tile_shared_entries = p->tiled.shared_entries;
+  info->tile_staged_rows = p->tiled.staged_rows;
   return ROF_OK;
 }
 

@@ -6,7 +6,7 @@ import numpy as np
 import torch
 import torch.nn.functional as F
 
-from .plan import AggregationPlan
+from .plan import AggregationPlan, scale_rows
 from .reuse_conv import ROF_GCNConv
 
 _TENSOR_FIELDS = ("row_pointers", "column_index", "degrees", "part_pointers", "part2Node", "part_cache_flagindex",
@@ -102,13 +102,16 @@ class ROF_GCN(torch.nn.Module):
 
 
 class SumAggregate(torch.autograd.Function):
-    """h -> self_scale * h + A h (sum or mean over in-neighbours) through an AggregationPlan, the
-    self term fused into the store of the gather kernel.  The backward pass applies the
-    transposed plan when given one, else the same plan (upstream's convention), with the same
-    fused self term."""
+    """h -> self_scale * h + A h (sum) or self_scale * h + D^-1 A h (mean) over in-neighbours through an
+    AggregationPlan, the self term fused into the store of the gather kernel.  The backward pass runs
+    the transposed plan when given one, else the same plan (upstream's convention: exact for a
+    symmetric graph).  For mean the gradient is A^T (D^-1 g): g is divided by the forward in-degrees
+    first and then summed, never averaged by the degrees again."""
 
     @staticmethod
     def forward(ctx, h, plan, plan_t, degrees, mode, self_scale=0.0):
+        if mode not in ("sum", "mean"):
+            raise ValueError("SumAggregate: mode must be 'sum' or 'mean'")
         ctx.plan_t, ctx.degrees, ctx.mode, ctx.self_scale = (plan_t or plan), degrees, mode, self_scale
         h = h.contiguous()
         return plan.aggregate(h, degrees, mode, tiles="auto", self_x=h if self_scale else None,
@@ -117,7 +120,8 @@ class SumAggregate(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         g = g.contiguous()
-        return (ctx.plan_t.aggregate(g, ctx.degrees, ctx.mode, tiles="auto", self_x=g if ctx.self_scale else None,
+        gs = scale_rows(g, ctx.degrees, "reciprocal") if ctx.mode == "mean" else g
+        return (ctx.plan_t.aggregate(gs, None, "sum", tiles="auto", self_x=g if ctx.self_scale else None,
                                      self_scale=ctx.self_scale), None, None, None, None, None)
 
 

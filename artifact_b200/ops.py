@@ -9,7 +9,12 @@ What differs from upstream, on purpose:
   for ROF_v1, a cudaDeviceSynchronize between its two kernels, reuse_conv_kernel.cu:689);
 * a graph without any reuse group (G = 0) works (upstream: "invalid configuration argument"
   then exit(-1), reuse_conv_kernel.cu:650-652, 709-714);
-* errors raise RuntimeError; the process is never killed.
+* errors raise RuntimeError; the process is never killed;
+* the GCN entry points hoist upstream's per-neighbour factor rsqrt(degrees[n]) (recomputed by every
+  lane for every neighbour, reuse_conv_kernel.cu:254, 914) into one pass over `tmp = X.W`
+  (`rof_scale_rows`) and aggregate in ROF_MODE_GCN_PRESCALED: the same products, one rsqrt per node;
+* `tmp` is allocated with a row stride padded to a multiple of 4 floats, so widths such as 7, 47
+  or 602 still run on 128-bit loads.
 
 Each distinct set of index tensors is turned into an AggregationPlan the first time it is
 seen and cached; the cache holds the tensors, so their addresses cannot be reused while the
@@ -19,7 +24,7 @@ from collections import OrderedDict
 
 import torch
 
-from .plan import AggregationPlan
+from .plan import AggregationPlan, padded_width, scale_rows
 
 _PLAN_CACHE = OrderedDict()
 _PLAN_CACHE_SIZE = 32
@@ -84,6 +89,28 @@ def _cache_arg(plan, part_result_cache, dim):
     return c
 
 
+def _transform_scaled(input, weight, degrees):
+    """tmp = rsqrt(degrees) * (input @ weight), rows padded to a multiple of 4 floats
+    (upstream: tmp = torch::mm(input, weight), reuse_conv_kernel.cu:302, 621, 971; the factor is
+    applied per neighbour inside its kernels)."""
+    d = weight.size(1)
+    ld = padded_width(d)
+    if ld != d:
+        w = torch.zeros((weight.size(0), ld), dtype=weight.dtype, device=weight.device)
+        w[:, :d] = weight
+        tmp = torch.mm(input, w)[:, :d]
+    else:
+        tmp = torch.mm(input, weight)
+    return scale_rows(tmp, degrees, "rsqrt", out=tmp)
+
+
+def _aligned_rows(x):
+    """x itself when its rows are 16-byte aligned, else a copy with a padded row stride"""
+    if x.size(1) % 4 == 0 and x.data_ptr() % 16 == 0:
+        return x
+    return scale_rows(x, None, "copy")
+
+
 def _backward_tail(d_input_prime, X, weight):
     # reuse_conv_kernel.cu:382-383 / 819-820 / 1050-1051
     d_input = torch.mm(d_input_prime, weight.transpose(0, 1))
@@ -97,7 +124,7 @@ def SAG(input, row_pointers, column_index, degrees, part_pointers, part2Node, pa
                  (degrees, "degrees"), (part_pointers, "part_pointers"), (part2Node, "part2Node")):
         _check_input(t, n)
     plan = plan_for_parts(input.size(0), column_index, part_pointers, part2Node)
-    return plan.aggregate(input, None, "sum", tiles="auto")
+    return plan.aggregate(_aligned_rows(input), None, "sum", tiles="auto")
 
 
 # ---- reuse_conv.cpp:158-205 ---------------------------------------------------------------
@@ -106,8 +133,8 @@ def GNNA_forward(input, weight, column_index, degrees, part_pointers, part2Node,
                  (part_pointers, "part_pointers"), (part2Node, "part2Node")):
         _check_input(t, n)
     plan = plan_for_parts(input.size(0), column_index, part_pointers, part2Node)
-    tmp = torch.mm(input, weight)                                   # reuse_conv_kernel.cu:302
-    return [plan.aggregate(tmp, degrees, "gcn", tiles="auto")]
+    tmp = _transform_scaled(input, weight, degrees)                 # reuse_conv_kernel.cu:302
+    return [plan.aggregate(tmp, degrees, "gcn_prescaled", tiles="auto")]
 
 
 def GNNA_backward(d_output, X, weight, column_index, degrees, part_pointers, part2Node, partSize, dimWorker,
@@ -116,7 +143,8 @@ def GNNA_backward(d_output, X, weight, column_index, degrees, part_pointers, par
                  (degrees, "degrees"), (part_pointers, "part_pointers"), (part2Node, "part2Node")):
         _check_input(t, n)
     plan = plan_for_parts(d_output.size(0), column_index, part_pointers, part2Node)
-    return _backward_tail(plan.aggregate(d_output, degrees, "gcn", tiles="auto"), X, weight)
+    ds = scale_rows(d_output, degrees, "rsqrt")
+    return _backward_tail(plan.aggregate(ds, degrees, "gcn_prescaled", tiles="auto"), X, weight)
 
 
 # ---- reuse_conv.cpp:208-285 ---------------------------------------------------------------
@@ -129,8 +157,9 @@ def reuse_forward_v1(input, weight, column_index, degrees, part_pointers, part2N
         _check_input(t, n)
     plan = plan_for_v1(input.size(0), column_index, part_pointers, part2Node, part_cache_flagindex,
                        part_pointers_cache, column_index_cache)
-    tmp = torch.mm(input, weight)                                   # reuse_conv_kernel.cu:621
-    return [plan.aggregate(tmp, degrees, "gcn", cache_result=_cache_arg(plan, part_result_cache, tmp.size(1)))]
+    tmp = _transform_scaled(input, weight, degrees)                 # reuse_conv_kernel.cu:621
+    return [plan.aggregate(tmp, degrees, "gcn_prescaled",
+                           cache_result=_cache_arg(plan, part_result_cache, tmp.size(1)))]
 
 
 def reuse_backward_v1(d_output, X, W, column_index, degrees, part_pointers, part2Node, partSize, dimWorker,
@@ -142,7 +171,9 @@ def reuse_backward_v1(d_output, X, W, column_index, degrees, part_pointers, part
         _check_input(t, n)
     plan = plan_for_v1(d_output.size(0), column_index, part_pointers, part2Node, part_cache_flagindex,
                        part_pointers_cache, column_index_cache)
-    dp = plan.aggregate(d_output, degrees, "gcn", cache_result=_cache_arg(plan, part_result_cache, d_output.size(1)))
+    ds = scale_rows(d_output, degrees, "rsqrt")
+    dp = plan.aggregate(ds, degrees, "gcn_prescaled",
+                        cache_result=_cache_arg(plan, part_result_cache, d_output.size(1)))
     return _backward_tail(dp, X, W)
 
 
@@ -154,8 +185,8 @@ def reuse_forward_v2(input, weight, uniqpart_column_index, degrees, uniqpart_poi
                  (part2Node_col, "part2Node_col")):
         _check_input(t, n)
     plan = plan_for_v2(input.size(0), uniqpart_column_index, uniqpart_pointers, part2Node_ptr, part2Node_col)
-    tmp = torch.mm(input, weight)                                   # reuse_conv_kernel.cu:971
-    return [plan.aggregate(tmp, degrees, "gcn", tiles="auto")]
+    tmp = _transform_scaled(input, weight, degrees)                 # reuse_conv_kernel.cu:971
+    return [plan.aggregate(tmp, degrees, "gcn_prescaled", tiles="auto")]
 
 
 def reuse_backward_v2(d_output, X, W, uniqpart_column_index, degrees, uniqpart_pointers, part2Node_ptr, part2Node_col,
@@ -165,4 +196,5 @@ def reuse_backward_v2(d_output, X, W, uniqpart_column_index, degrees, uniqpart_p
                  (part2Node_col, "part2Node_col")):
         _check_input(t, n)
     plan = plan_for_v2(d_output.size(0), uniqpart_column_index, uniqpart_pointers, part2Node_ptr, part2Node_col)
-    return _backward_tail(plan.aggregate(d_output, degrees, "gcn", tiles="auto"), X, W)
+    ds = scale_rows(d_output, degrees, "rsqrt")
+    return _backward_tail(plan.aggregate(ds, degrees, "gcn_prescaled", tiles="auto"), X, W)

@@ -12,7 +12,8 @@ import torch
 
 from . import _native
 
-MODES = {"gcn": 0, "sum": 1, "mean": 2}
+MODES = {"gcn": 0, "sum": 1, "mean": 2, "gcn_prescaled": 3}
+SCALE_OPS = {"copy": 0, "rsqrt": 1, "reciprocal": 2}
 _PHASE_NAMES = {1: "rof:partials", 2: "rof:gather", 4: "rof:segment_reduce", 7: "rof:aggregate"}
 # ROF_NVTX=1 brackets every C-ABI aggregation call with an NVTX range (visible to ncu --nvtx)
 _NVTX = os.environ.get("ROF_NVTX", "0") not in ("", "0")
@@ -41,6 +42,64 @@ def _same_place(parts):
     if len(wh) != 1:
         raise RuntimeError("all index tensors of one layout must live in the same place (all host or all device)")
     return wh.pop()
+
+
+def padded_width(dim):
+    """leading dimension (floats) that keeps every row of a [*, dim] fp32 matrix 16-byte aligned"""
+    return (int(dim) + 3) // 4 * 4
+
+
+def empty_padded(rows, dim, device):
+    """A [rows, dim] fp32 view whose row stride is padded to a multiple of 4 floats, so that the
+    gather kernels can use 128-bit loads (and the shared-memory ring) whatever `dim` is."""
+    return torch.empty((rows, padded_width(dim)), dtype=torch.float32, device=device)[:, :dim]
+
+
+def scale_rows(x, degrees, op="rsqrt", out=None):
+    """rof_scale_rows(): out[r] = f(degrees[r]) * x[r] (f: 'copy', 'rsqrt', 'reciprocal').  With
+    out=None the result goes to a new padded buffer (see empty_padded); out may be x (in place)."""
+    if not x.is_cuda or x.dtype != torch.float32 or x.dim() != 2 or (x.stride(1) != 1 and x.size(1) > 1):
+        raise RuntimeError("x must be a 2-D float32 CUDA tensor with unit column stride")
+    rows, dim = x.shape
+    if out is None:
+        out = empty_padded(rows, dim, x.device)
+    elif (tuple(out.shape) != (rows, dim) or out.dtype != torch.float32 or out.device != x.device
+          or (out.stride(1) != 1 and dim > 1)):
+        raise RuntimeError("out must be a float32 tensor like x with unit column stride")
+    deg_ptr = None
+    if SCALE_OPS[op] != 0:
+        if (degrees is None or degrees.device != x.device or degrees.dtype != torch.float32
+                or not degrees.is_contiguous() or degrees.numel() < rows):
+            raise RuntimeError("degrees must be a contiguous float32 tensor on x's device with one entry per row")
+        deg_ptr = ctypes.c_void_p(degrees.data_ptr())
+    with _device_guard(x.device):
+        _native.check(_native.cuda().rof_scale_rows(
+            ctypes.c_void_p(x.data_ptr()), x.stride(0) if rows > 1 else dim, dim, deg_ptr, SCALE_OPS[op],
+            ctypes.c_void_p(out.data_ptr()), out.stride(0) if rows > 1 else padded_width(dim), rows,
+            ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)))
+    return out
+
+
+def probe_read_gbs(nbytes, device, repeats=None, iters=5):
+    """Read bandwidth in GB/s of a coalesced 128-bit streaming kernel over a `nbytes` buffer
+    (rof_probe_read): L2 -> SM when the buffer fits L2, HBM when it is much larger."""
+    buf = torch.zeros(nbytes // 4, dtype=torch.float32, device=device)
+    sink = torch.zeros(1, dtype=torch.float32, device=device)
+    repeats = repeats or max(1, int(4e9 // nbytes))
+    lib = _native.cuda()
+    best = 0.0
+    with _device_guard(device):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+        for i in range(iters + 1):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _native.check(lib.rof_probe_read(ctypes.c_void_p(buf.data_ptr()), nbytes, repeats,
+                                             ctypes.c_void_p(sink.data_ptr()), stream))
+            e1.record()
+            torch.cuda.synchronize(device)
+            if i:                                   # the first run warms the cache
+                best = max(best, nbytes * repeats / (e0.elapsed_time(e1) / 1e3) / 1e9)
+    return best
 
 
 class AggregationPlan:
@@ -154,6 +213,16 @@ class AggregationPlan:
                                                      p(out["group_col"]), p(out["items"]), p(out["split_rows"])))
         return out
 
+    def export_tiles(self):
+        """shared-memory tiles of the plan (rof_plan_export_tiles); empty arrays when it has none"""
+        i = self.info
+        out = {"tiles": np.zeros((i["num_tiles"], 4), np.int32), "titems": np.zeros((i["tile_items"], 4), np.int32),
+               "tcol": np.zeros(i["tile_entries"], np.int32), "stage_col": np.zeros(i["num_tiles"] * 64, np.int32)}
+        p = lambda a: ctypes.c_void_p(a.ctypes.data)
+        _native.check(_native.cuda().rof_plan_export_tiles(self._h, p(out["tiles"]), p(out["titems"]), p(out["tcol"]),
+                                                           p(out["stage_col"])))
+        return out
+
     def workspace_bytes(self, dim):
         return int(_native.cuda().rof_plan_workspace_bytes(self._h, int(dim)))
 
@@ -236,14 +305,14 @@ class AggregationPlan:
             if accumulate:
                 raise RuntimeError("accumulate=True adds to an existing `out`")
             out = torch.empty((rows, dim), dtype=torch.float32, device=x.device)
-        elif (out.dtype != torch.float32 or not out.is_cuda or out.dim() != 2 or out.size(0) != rows
-              or out.size(1) != dim or (out.stride(1) != 1 and dim > 1)):
-            raise RuntimeError("out must be a float32 CUDA tensor of shape [rows, dim] with unit column stride")
+        else:
+            self._check_out(out, rows, dim, x.device)
         m = MODES[mode]
         deg_ptr = None
         if m != MODES["sum"]:
-            if degrees is None or not degrees.is_cuda or degrees.dtype != torch.float32 or not degrees.is_contiguous():
-                raise RuntimeError("degrees must be a contiguous float32 CUDA tensor")
+            if (degrees is None or degrees.device != x.device or degrees.dtype != torch.float32
+                    or not degrees.is_contiguous()):
+                raise RuntimeError("degrees must be a contiguous float32 CUDA tensor on x's device")
             if degrees.numel() != i["num_nodes"]:
                 raise RuntimeError("degrees must have one entry per node")
             deg_ptr = ctypes.c_void_p(degrees.data_ptr())
@@ -298,6 +367,16 @@ class AggregationPlan:
                     gather_events.append((e0, e1))
         return out
 
+    @staticmethod
+    def _check_out(out, rows, dim, device):
+        if (out.dtype != torch.float32 or out.device != device or out.dim() != 2 or out.size(0) != rows
+                or out.size(1) != dim or (out.stride(1) != 1 and dim > 1)):
+            raise RuntimeError("out must be a float32 tensor of shape [rows, dim] with unit column stride on x's device")
+
+    def take_status(self):
+        """non-zero when a bounded wait inside a kernel of an earlier pass ran out (rof_plan_take_status)"""
+        return int(_native.cuda().rof_plan_take_status(self._h))
+
     def aggregate_static_scratch(self, x, degrees=None, mode="gcn", out=None):
         """rof_aggregate_static_scratch(): the same pass with the library's built-in 32 MiB scratch
         instead of a workspace, for callers that cannot allocate device memory at call time.  Here
@@ -311,12 +390,13 @@ class AggregationPlan:
         dim, rows = x.size(1), i["row_end"] - i["row_begin"]
         if out is None:
             out = torch.empty((rows, dim), dtype=torch.float32, device=x.device)
-        elif tuple(out.shape) != (rows, dim) or out.dtype != torch.float32 or not out.is_cuda:
-            raise RuntimeError("out must be a float32 CUDA tensor of shape [rows, dim]")
+        else:
+            self._check_out(out, rows, dim, x.device)
         deg_ptr = None
         if MODES[mode] != MODES["sum"]:
-            if degrees is None or not degrees.is_cuda or degrees.dtype != torch.float32 or degrees.numel() != i["num_nodes"]:
-                raise RuntimeError("degrees must be a float32 CUDA tensor with one entry per node")
+            if (degrees is None or degrees.device != x.device or degrees.dtype != torch.float32
+                    or not degrees.is_contiguous() or degrees.numel() != i["num_nodes"]):
+                raise RuntimeError("degrees must be a contiguous float32 tensor on x's device with one entry per node")
             deg_ptr = ctypes.c_void_p(degrees.data_ptr())
         with _device_guard(x.device):
             _native.check(_native.cuda().rof_aggregate_static_scratch(

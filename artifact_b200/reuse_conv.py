@@ -145,6 +145,6 @@ class ROF_GCNConv(torch.nn.Module):
         else:
             raise NotImplementedError
         with torch.no_grad():
-            tmp = torch.mm(x, self.weight)
-            return plan.aggregate(tmp, info.degrees, "gcn", tiles="auto",
+            tmp = ROF._transform_scaled(x, self.weight, info.degrees)
+            return plan.aggregate(tmp, info.degrees, "gcn_prescaled", tiles="auto",
                                   bias=self.bias.detach() if self.bias is not None else None, relu=relu)

@@ -34,7 +34,7 @@ enum rof_status {
   ROF_ERR_CUDA = 3,           /* a CUDA runtime call failed; see rof_last_error() */
   ROF_ERR_WORKSPACE = 4,      /* workspace missing, misaligned or smaller than rof_plan_workspace_bytes() */
   ROF_ERR_NO_MEMORY = 5,      /* host allocation failed while building a plan */
-  ROF_ERR_WAIT_LIMIT = 6      /* a bounded device-side wait gave up (reserved for the multi-GPU pipeline) */
+  ROF_ERR_WAIT_LIMIT = 6      /* a bounded device-side wait (shared-memory ring copies) gave up */
 };
 
 /* What is summed.  Upstream implements GCN (its GNNA / ROF_v1 / ROF_v2 kernels,
@@ -43,7 +43,12 @@ enum rof_status {
 enum rof_mode {
   ROF_MODE_GCN = 0,  /* out[v] = rsqrt(deg[v]) * sum_n rsqrt(deg[n]) * x[n] */
   ROF_MODE_SUM = 1,  /* out[v] = sum_n x[n] */
-  ROF_MODE_MEAN = 2  /* out[v] = (sum_n x[n]) / deg[v] */
+  ROF_MODE_MEAN = 2, /* out[v] = (sum_n x[n]) / deg[v] */
+  /* GCN over rows the caller already multiplied by rsqrt(deg[n]) (rof_scale_rows):
+   * out[v] = rsqrt(deg[v]) * sum_n x[n].  Same products as ROF_MODE_GCN — upstream multiplies
+   * inside its kernels, once per lane per neighbour (reuse_conv_kernel.cu:254, 914) — without
+   * the degree load and the rsqrt per gathered row. */
+  ROF_MODE_GCN_PRESCALED = 3
 };
 
 enum rof_location { ROF_ON_HOST = 0, ROF_ON_DEVICE = 1 };
@@ -61,6 +66,11 @@ typedef struct rof_plan_info {
   int64_t split_rows;       /* rows cut into segments (second-stage reduce) */
   int64_t num_slots;        /* segment sums held in scratch between phase B and the reduce */
   int64_t segment_edges;    /* maximum entries per work item */
+  int64_t num_tiles;            /* shared-memory tiles of short rows (0: the plan has none) */
+  int64_t tile_items;           /* rows covered by tiles */
+  int64_t tile_entries;         /* their entries */
+  int64_t tile_shared_entries;  /* of which are read from shared memory instead of global memory */
+  int64_t tile_staged_rows;     /* rows copied into shared memory, summed over the tiles */
 } rof_plan_info;
 
 /*
@@ -116,6 +126,22 @@ int rof_plan_get_info(const rof_plan* plan, rof_plan_info* info);
  */
 int rof_plan_export(const rof_plan* plan, int64_t* row_ptr, int32_t* col, int32_t* group_ptr,
                     int32_t* group_col, int32_t* items, int32_t* split_rows);
+
+/*
+ * Shared-memory tiles of a plan (inspection; any pointer may be NULL).  Where the short rows of a
+ * graph share many of their entries — reuse groups fanned out to neighbouring destinations, the
+ * regime upstream's partial-sum reuse is built for (reuse_conv_kernel.cu:902-952) — the plan groups
+ * 32 consecutive short rows into a tile and lists the entries used at least twice inside it; the
+ * tile kernel stages those rows once in shared memory and every destination of the tile adds them
+ * from there.
+ *   tiles     [num_tiles][4]   int32  (first_item, num_items, stage_begin, stage_count)
+ *   titems    [tile_items][4]  int32  (begin, end, dst, mid) into tcol: [begin,mid) slot numbers of
+ *                                      the tile's staged rows, [mid,end) global ids (as in `col`)
+ *   tcol      [tile_entries]   int32
+ *   stage_col [num_tiles * 64] int32  ids of the rows staged by each tile (stage_count valid per tile)
+ */
+int rof_plan_export_tiles(const rof_plan* plan, int32_t* tiles, int32_t* titems, int32_t* tcol,
+                          int32_t* stage_col);
 
 /*
  * Staged plans for the multi-GPU pipeline (no upstream counterpart: upstream is single-GPU).
@@ -207,6 +233,32 @@ int rof_aggregate_fused(const rof_plan* plan, int phases, int mode, const float*
 #define ROF_STATIC_SCRATCH_BYTES (32u << 20)
 int rof_aggregate_static_scratch(const rof_plan* plan, int mode, const float* x, int64_t ldx, int dim,
                                  const float* degrees, float* out, int64_t ldo, void* stream);
+
+/*
+ * Row scaling pass in front of an aggregation: out[r][0:dim] = f(degrees[r]) * x[r][0:dim] for
+ * r in [0, num_rows), f = 1 (ROF_SCALE_COPY), rsqrt (ROF_SCALE_RSQRT) or reciprocal, 0 for a
+ * zero degree (ROF_SCALE_RECIPROCAL).  `out` may be `x` itself (in place) or a buffer with a
+ * padded leading dimension; columns [dim, min(ldo, dim rounded up to 4)) of out are zeroed.
+ * With ROF_SCALE_RSQRT it hoists upstream's per-neighbour factor rsqrt(degrees[n])
+ * (reuse_conv_kernel.cu:254, 270) out of the gather: follow with ROF_MODE_GCN_PRESCALED.
+ */
+enum rof_scale_op { ROF_SCALE_COPY = 0, ROF_SCALE_RSQRT = 1, ROF_SCALE_RECIPROCAL = 2 };
+int rof_scale_rows(const float* x, int64_t ldx, int dim, const float* degrees, int op, float* out, int64_t ldo,
+                   int64_t num_rows, void* stream);
+
+/*
+ * Bandwidth probe (measurement aid, no upstream counterpart): streams `bytes` of device memory
+ * `repeats` times through 128-bit loads that bypass L1 and discards the sum.  With a buffer that
+ * fits L2 this measures the L2 -> SM read bandwidth the gather kernels are bounded by when the
+ * feature rows are L2-resident; with a buffer much larger than L2, the HBM read bandwidth.
+ * `sink` is one device float the kernel may write.
+ */
+int rof_probe_read(const void* buffer, int64_t bytes, int repeats, float* sink, void* stream);
+
+/* Reads and clears the plan's device status word: non-zero when a bounded wait inside a kernel
+ * of an earlier pass ran out (that pass's output is incomplete).  rof_aggregate() checks it on
+ * entry and returns ROF_ERR_WAIT_LIMIT. */
+int rof_plan_take_status(rof_plan* plan);
 
 /* Number of kernel launches the last rof_aggregate() on this thread enqueued. */
 int rof_last_launch_count(void);

@@ -183,3 +183,34 @@ def test_eval_mode_fused_bias_relu_equals_training_path(kernel_type):
     with torch.no_grad():
         fused = model(x, info)                              # inference path: fused into the gather's store
     assert_close(fused.cpu().numpy(), unfused.cpu().numpy(), what="fused bias/ReLU vs separate passes")
+
+
+@pytest.mark.parametrize("mode", ["sum", "mean"])
+def test_sum_aggregate_gradient_matches_dense_autograd(mode):
+    """h -> s*h + A h (sum) and s*h + D^-1 A h (mean) on a directed graph with the transposed plan:
+    the gradient must be s*g + A^T g and s*g + A^T D^-1 g (degrees differ per node, so a mean
+    gradient that divides by the degrees on the wrong side shows up)"""
+    from artifact_b200.models import SumAggregate
+    g = graphs.config2(400 / 232965)
+    n = g.num_nodes
+    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(DEV)
+    ids = torch.arange(n, dtype=torch.int32, device=DEV)
+    plan = AggregationPlan.from_parts(n, i32(g.indices_src), i32(g.indptr_dst), ids)
+    plan_t = AggregationPlan.from_parts(n, i32(g.indices_dst), i32(g.indptr_src), ids)
+    deg = torch.from_numpy(g.degrees_f32()).to(DEV)
+    A = torch.zeros((n, n), dtype=torch.float64)
+    A[np.repeat(np.arange(n), np.diff(g.indptr_dst)), g.indices_src] = 1.0
+    if mode == "mean":
+        inv = torch.where(deg > 0, 1.0 / deg.double(), torch.zeros_like(deg, dtype=torch.float64)).cpu()
+        A = inv[:, None] * A
+    A = A.to(DEV)
+    torch.manual_seed(8)
+    h = torch.randn((n, 9), device=DEV, requires_grad=True)
+    w = torch.randn((n, 9), device=DEV)
+    y = SumAggregate.apply(h, plan, plan_t, deg, mode, 0.5)
+    (y * w).sum().backward()
+    hd = h.detach().double().requires_grad_()
+    yd = 0.5 * hd + A @ hd
+    (yd * w.double()).sum().backward()
+    assert_close(y.detach().cpu().numpy(), yd.detach().cpu().numpy(), what=f"{mode} forward")
+    assert_close(h.grad.cpu().numpy(), hd.grad.cpu().numpy(), what=f"{mode} gradient")

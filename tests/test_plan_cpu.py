@@ -196,3 +196,53 @@ def test_fuzz_plans_and_oracle_on_random_graphs():
         v2 = rof_oracle.aggregate_v2(x, L["uniqpart_column_index"], deg, L["uniqpart_pointers"], L["part2Node_ptr"],
                                      L["part2Node_col"], "gcn", True)
         assert np.allclose(v1, base, rtol=1e-6, atol=1e-6) and np.allclose(v2, base, rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("which", ["parts", "v2"])
+def test_tiles_hold_the_same_rows(golden, which, monkeypatch):
+    """shared-memory tiles (forced on): every tiled row must expand to exactly the entries of the
+    plan's row — staged slots through the tile's stage list plus the rows read from global
+    memory — every staged id must occur at least twice in its tile, and rows and tiles must be
+    covered once"""
+    monkeypatch.setenv("ROF_TILES", "1")
+    N = golden["N"]
+    plan = BUILDERS[which](N, *layout_args(golden["layouts"], which))
+    ex, tl = plan.export(), plan.export_tiles()
+    info = plan.info
+    assert info["num_tiles"] == len(tl["tiles"]) > 0
+    lens = np.diff(ex["row_ptr"])
+    short = np.flatnonzero(lens <= 256)
+    assert info["tile_items"] == len(short)
+    seen, shared = [], 0
+    for t, (first, count, sb, sc) in enumerate(tl["tiles"]):
+        assert 0 < count <= 32 and 0 <= sc <= 64 and sb == t * 64
+        stage = tl["stage_col"][sb:sb + sc]
+        assert len(set(stage.tolist())) == sc
+        occurrences = {}
+        for b, e, dst, mid in tl["titems"][first:first + count]:
+            seen.append(dst)
+            slots, glob = tl["tcol"][b:mid], tl["tcol"][mid:e]
+            assert (slots >= 0).all() and (slots < sc).all()
+            assert not set(glob.tolist()) & set(stage.tolist()), "a staged id is also read from global memory"
+            got = sorted(stage[slots].tolist() + glob.tolist())
+            want = sorted(ex["col"][ex["row_ptr"][dst]:ex["row_ptr"][dst + 1]].tolist())
+            assert got == want, (which, dst)
+            shared += len(slots)
+            for c in stage[slots]:
+                occurrences[int(c)] = occurrences.get(int(c), 0) + 1
+        assert all(v >= 2 for v in occurrences.values()) and len(occurrences) == sc
+    assert sorted(seen) == short.tolist()
+    assert info["tile_shared_entries"] == shared and info["tile_entries"] == int(lens[short].sum())
+
+
+def test_tiles_are_built_only_where_rows_share_entries(monkeypatch):
+    """unset ROF_TILES: the community fixture (neighbouring rows share a pool of sources) gets tiles,
+    the power-law fixture does not; ROF_TILES=0 never builds them"""
+    from conftest import load_golden
+    monkeypatch.delenv("ROF_TILES", raising=False)
+    c5, c2 = load_golden("c5_n1024_ps2"), load_golden("c2_n640_ps2")
+    assert AggregationPlan.from_v2(c5["N"], *layout_args(c5["layouts"], "v2")).info["num_tiles"] > 0
+    assert AggregationPlan.from_parts(c5["N"], *layout_args(c5["layouts"], "parts")).info["num_tiles"] > 0
+    assert AggregationPlan.from_v2(c2["N"], *layout_args(c2["layouts"], "v2")).info["num_tiles"] == 0
+    monkeypatch.setenv("ROF_TILES", "0")
+    assert AggregationPlan.from_v2(c5["N"], *layout_args(c5["layouts"], "v2")).info["num_tiles"] == 0
