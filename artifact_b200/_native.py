@@ -77,6 +77,8 @@ CUDA_ABI = [
     ("rof_plan_create_v2", c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_int, c_int, c_void_p, c_int64,
                                    c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     ("rof_plan_create_stages", c_int, [c_void_p, c_int, c_void_p, c_int, c_int, ctypes.POINTER(c_void_p), c_void_p]),
+    ("rof_plan_create_stages_ranges", c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.POINTER(c_void_p),
+                                              c_void_p]),
     ("rof_plan_destroy", None, [c_void_p]),
     ("rof_plan_get_info", c_int, [c_void_p, ctypes.POINTER(PlanInfo)]),
     ("rof_plan_export", c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),

@@ -31,13 +31,13 @@ inline bool fuse_reduce_enabled() {
   return v;
 }
 
-// Host policy for the gather kernels (see kernels.cu): plans whose work items are short run the
-// pipelined warp-per-item kernel, everything else the lane-group kernel.  The shared-memory ring
-// kernel measured about half as fast as either on B200 (one bulk copy per row of at most a few
-// KB does not keep the copy engine busy) and is only used on request (ROF_KERNEL=ring).
+// Host policy for the gather kernels (see kernels.cu): the lane-group kernel.  The shared-memory
+// ring kernel measured about half as fast on B200 at every width tried (one bulk copy per row
+// of at most a few KB does not keep the copy engine busy) and is only used on request
+// (ROF_KERNEL=ring).
 inline int kernel_for(int num_items, int64_t entries) {
-  if (num_items <= 0) return 0;
-  return ((double)entries / num_items < rof::kShortItemEntries) ? 2 : 0;
+  (void)num_items; (void)entries;
+  return 0;
 }
 
 inline bool use_fine_cut(const rof_plan* p, int dim) { return p->fine.num_items > 0 && dim <= rof::kNarrowRowFloats; }

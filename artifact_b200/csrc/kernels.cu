@@ -1,31 +1,36 @@
 // Gather kernels for sm_100a.
 //
-// Two kernels sum the rows a work item names — a destination row, one segment of a long
-// destination row, or one reuse group — and both keep the accumulators in registers and store
-// every output row exactly once, so there are no atomics on data and no zero-fill pass
-// (upstream: atomicAdd_F per element per part and a torch::zeros per call,
-// reuse_conv_kernel.cu:16-21, 282, 303).
+// Three kernels sum the rows a work item names — a destination row, one segment of a long
+// destination row, or one reuse group.  All keep the accumulators in registers and store every
+// output row exactly once, so there are no atomics on data and no zero-fill pass (upstream:
+// atomicAdd_F per element per part and a torch::zeros per call, reuse_conv_kernel.cu:16-21, 282,
+// 303).
 //
 // gather_rows_kernel ("lanes"): a *lane group* of L threads (L = 4..32, a power of two chosen
 // from the feature width) owns one work item.  The group fetches L column entries with one
 // coalesced load, broadcasts them with shuffles, and issues U independent 128-bit (64/32-bit
 // when alignment forces it) row loads per lane before accumulating, so each warp keeps
 // U*C*16 B per lane in flight.  An item's entries are ordered [partial rows | feature rows] so
-// each range has one base pointer, the unweighted modes do no multiply, and full batches run
-// without per-entry predicates.
+// each range has one base pointer, the unweighted modes do no multiply, and no load slot is
+// issued for an entry that does not exist.  Adds and multiply-adds are the packed f32x2
+// instructions of sm_100.
+//
+// gather_tiles_kernel ("tiles"): for short rows that share many of their entries with their
+// neighbours.  One CTA owns a tile of consecutive destination rows, copies the rows used at
+// least twice in the tile — partial-sum rows of reuse groups fanned out to these destinations,
+// shared feature rows — into shared memory once, and every destination adds them from there;
+// only the rows private to a destination are gathered from global memory.
 //
 // gather_rows_ring_kernel ("ring"): one warp owns one work item and a ring of shared-memory
-// stages.  Every gathered row — feature row or partial-sum row of a reuse group — is brought
-// into the ring by one bulk asynchronous copy (cp.async.bulk global -> shared, completion
-// counted on an mbarrier per stage; the lane that holds a column entry issues that row's copy),
-// and the warp adds rows from shared memory into its register accumulators while the copies of
-// the next stages are in flight.  Per SM this keeps the whole ring (up to ~200 KB) in flight
-// instead of what fits in registers, and a row costs one instruction to request instead of one
-// load per lane.  Rows must be 16-byte aligned (leading dimensions that are multiples of 4
-// floats).  Upstream keeps each part's partial sum in shared memory too, but fills it with
-// scalar loads and read-modify-writes per neighbour (reuse_conv_kernel.cu:902-935).
-// Every wait on an mbarrier is bounded: a wait that runs out sets the plan's status word,
-// the warp waits (bounded again) for its copies in flight and leaves without storing.
+// stages.  Every gathered row is brought into the ring by one bulk asynchronous copy
+// (cp.async.bulk global -> shared, completion counted on an mbarrier per stage; the lane that
+// holds a column entry issues that row's copy), and the warp adds rows from shared memory into its
+// register accumulators while the copies of the next stages are in flight.  Rows must be
+// 16-byte aligned.  Measured about half as fast as the lanes kernel on B200 at every width tried
+// — a bulk copy per row of at most a few KB does not keep the copy engine busy — so it only
+// runs on request (ROF_KERNEL=ring).  Every wait on an mbarrier is bounded: a wait that runs out
+// sets the plan's status word, the warp waits (bounded again) for its copies in flight and
+// leaves without storing.
 //
 // Rows whose work was cut into segments are finished by whichever segment arrives last (a
 // per-row arrival counter); it adds the segment sums in slot order, so the result does not
@@ -191,85 +196,112 @@ __device__ __forceinline__ void reduce_split_row(const GatherArgs& a, const Spli
   }
 }
 
-// acc += sum over col[begin, end) of (WEIGHTED ? rsqrt(degrees[c]) : 1) * row(c), where
-// row(c) starts at base_lane + (c - c_offset) * ld (base_lane already includes this lane's
-// column offset).  `active[k]` says whether this lane's k-th vector lies inside the row.
-template <int VEC, int L, int C, int U, bool WEIGHTED>
+// acc += v and acc += w * v on VEC consecutive floats.  Pairs of floats go through the packed
+// f32x2 instructions of sm_100 (one instruction per two adds; each half rounds like the scalar
+// instruction, so results do not change).
+template <int VEC>
+__device__ __forceinline__ void acc_add(float (&acc)[VEC], const float (&v)[VEC]) {
+  if constexpr (VEC == 1) {
+    acc[0] = __fadd_rn(acc[0], v[0]);
+  } else {
+#pragma unroll
+    for (int t = 0; t < VEC; t += 2) {
+      const float2 r = __fadd2_rn(make_float2(acc[t], acc[t + 1]), make_float2(v[t], v[t + 1]));
+      acc[t] = r.x; acc[t + 1] = r.y;
+    }
+  }
+}
+
+template <int VEC>
+__device__ __forceinline__ void acc_fma(float (&acc)[VEC], float w, const float (&v)[VEC]) {
+  if constexpr (VEC == 1) {
+    acc[0] = __fmaf_rn(w, v[0], acc[0]);
+  } else {
+#pragma unroll
+    for (int t = 0; t < VEC; t += 2) {
+      const float2 r = __ffma2_rn(make_float2(w, w), make_float2(v[t], v[t + 1]), make_float2(acc[t], acc[t + 1]));
+      acc[t] = r.x; acc[t + 1] = r.y;
+    }
+  }
+}
+
+// Where the rows of one range of entries live.  Plain: every entry c names row (c - c_offset)
+// of one buffer.  MIXED (tile kernel): entries >= num_nodes name partial rows, the others feature
+// rows, selected per entry.  Pointers already include this lane's column offset.
+struct RowSource {
+  const float* base; int64_t ld; int c_offset;      // plain
+  const float* partials; int64_t ldp; int num_nodes;  // MIXED only
+};
+
+// Loads UU rows — entries j .. j+UU-1 of the window of L entries the group holds in `c` (and
+// their weights in `w`) — and adds them to acc.  No per-entry predicate: the caller only asks for
+// entries that exist.
+template <int VEC, int L, int C, int UU, bool WEIGHTED, bool MIXED>
+__device__ __forceinline__ void gather_batch(float (&acc)[C][VEC], int c, float w, int j, const RowSource& src,
+                                             unsigned gmask, const bool (&active)[C], int lane_vec0) {
+  float v[UU][C][VEC];
+#pragma unroll
+  for (int u = 0; u < UU; ++u) {
+    const int cj = __shfl_sync(gmask, c, j + u, L);
+    const float* rp;
+    if constexpr (MIXED)
+      rp = (cj >= src.num_nodes) ? src.partials + (int64_t)(cj - src.num_nodes) * src.ldp : src.base + (int64_t)cj * src.ld;
+    else
+      rp = src.base + (int64_t)cj * src.ld;
+#pragma unroll
+    for (int k = 0; k < C; ++k) {
+      if (active[k]) {
+        load_row_vec<VEC>(v[u][k], rp + k * (L * VEC));
+      } else {
+#pragma unroll
+        for (int t = 0; t < VEC; ++t) v[u][k][t] = 0.0f;
+      }
+    }
+  }
+  (void)lane_vec0;
+#pragma unroll
+  for (int u = 0; u < UU; ++u) {
+    if constexpr (WEIGHTED) {
+      const float wj = __shfl_sync(gmask, w, j + u, L);
+#pragma unroll
+      for (int k = 0; k < C; ++k) acc_fma<VEC>(acc[k], wj, v[u][k]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < C; ++k) acc_add<VEC>(acc[k], v[u][k]);
+    }
+  }
+}
+
+// acc += sum over col[begin, end) of (WEIGHTED ? rsqrt(degrees[c]) : 1) * row(c).  The group
+// fetches L entries at a time and walks them in batches of U rows; what is left of a window
+// is walked in batches of 4, 2 and 1, so that no load slot is issued for an entry that does
+// not exist (short rows are bound by instruction issue as much as by latency).
+template <int VEC, int L, int C, int U, bool WEIGHTED, bool MIXED>
 __device__ __forceinline__ void accumulate_range(float (&acc)[C][VEC], const int32_t* __restrict__ col, int begin,
-                                                 int end, const float* base_lane, int64_t ld, int c_offset,
-                                                 const float* __restrict__ degrees, int lane, unsigned gmask,
-                                                 const bool (&active)[C]) {
+                                                 int end, const RowSource& src, const float* __restrict__ degrees,
+                                                 int lane, unsigned gmask, const bool (&active)[C]) {
   for (int e = begin; e < end; e += L) {
     const int mine = e + lane;
     int c = 0;
     float w = 1.0f;
     if (mine < end) {
       c = __ldg(col + mine);
-      if constexpr (WEIGHTED) w = __frsqrt_rn(__ldg(degrees + c));
-      c -= c_offset;
+      if constexpr (WEIGHTED) {
+        if (!MIXED || c < src.num_nodes) w = __frsqrt_rn(__ldg(degrees + c));
+      }
+      if constexpr (!MIXED) c -= src.c_offset;
     }
     const int cnt = min(L, end - e);
     int j = 0;
-    for (; j + U <= cnt; j += U) {  // full batches: no per-entry predicate
-      float v[U][C][VEC];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int cj = __shfl_sync(gmask, c, j + u, L);
-        const float* rp = base_lane + (int64_t)cj * ld;
-#pragma unroll
-        for (int k = 0; k < C; ++k) {
-          if (active[k]) {
-            load_row_vec<VEC>(v[u][k], rp + k * (L * VEC));
-          } else {
-#pragma unroll
-            for (int t = 0; t < VEC; ++t) v[u][k][t] = 0.0f;
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        float wj = 1.0f;
-        if constexpr (WEIGHTED) wj = __shfl_sync(gmask, w, j + u, L);
-#pragma unroll
-        for (int k = 0; k < C; ++k)
-#pragma unroll
-          for (int t = 0; t < VEC; ++t) {
-            if constexpr (WEIGHTED) acc[k][t] = __fmaf_rn(wj, v[u][k][t], acc[k][t]);
-            else acc[k][t] = __fadd_rn(acc[k][t], v[u][k][t]);
-          }
-      }
+    for (; j + U <= cnt; j += U) gather_batch<VEC, L, C, U, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane);
+    if constexpr (U > 4) {
+      if (cnt - j >= 4) { gather_batch<VEC, L, C, 4, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane); j += 4; }
     }
-    if (j < cnt) {  // the last, partial batch of the range: same shape, predicated per entry
-      float v[U][C][VEC];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int cj = __shfl_sync(gmask, c, j + u, L);
-        const bool ok = (j + u) < cnt;
-        const float* rp = base_lane + (int64_t)cj * ld;
-#pragma unroll
-        for (int k = 0; k < C; ++k) {
-          if (ok && active[k]) {
-            load_row_vec<VEC>(v[u][k], rp + k * (L * VEC));
-          } else {
-#pragma unroll
-            for (int t = 0; t < VEC; ++t) v[u][k][t] = 0.0f;
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        float wj = 1.0f;
-        if constexpr (WEIGHTED) wj = __shfl_sync(gmask, w, j + u, L);
-        if ((j + u) < cnt) {
-#pragma unroll
-          for (int k = 0; k < C; ++k)
-#pragma unroll
-            for (int t = 0; t < VEC; ++t) {
-              if constexpr (WEIGHTED) acc[k][t] = __fmaf_rn(wj, v[u][k][t], acc[k][t]);
-              else acc[k][t] = __fadd_rn(acc[k][t], v[u][k][t]);
-            }
-        }
-      }
+    if constexpr (U > 2) {
+      if (cnt - j >= 2) { gather_batch<VEC, L, C, 2, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane); j += 2; }
+    }
+    if constexpr (U > 1) {
+      if (cnt - j >= 1) gather_batch<VEC, L, C, 1, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane);
     }
   }
 }
@@ -316,7 +348,7 @@ __device__ __forceinline__ void finish_segment(const GatherArgs& a, int slot, fl
 // VEC floats per load, L lanes per item, C vectors per lane (L*C*VEC >= dim), U rows in flight;
 // WEIGHTED: multiply each feature row by rsqrt(degrees[col]) (GCN).
 template <int VEC, int L, int C, int U, bool WEIGHTED>
-__global__ void __launch_bounds__(256, (C <= 2 ? 4 : 1)) gather_rows_kernel(const __grid_constant__ GatherArgs a) {
+__global__ void __launch_bounds__(256, (C <= 2 ? 4 : (C * U <= 6 ? 3 : (C * U <= 12 ? 2 : 1)))) gather_rows_kernel(const __grid_constant__ GatherArgs a) {
   static_assert(U <= L && (L % U) == 0, "a batch of L entries is a whole number of unrolled steps");
   const int64_t gtid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int item_id = (int)(gtid / L);
@@ -338,12 +370,14 @@ __global__ void __launch_bounds__(256, (C <= 2 ? 4 : 1)) gather_rows_kernel(cons
     for (int t = 0; t < VEC; ++t) acc[k][t] = 0.0f;
   }
 
-  if (mid > begin)
-    accumulate_range<VEC, L, C, U, false>(acc, a.col, begin, mid, a.partials + lane * VEC, a.ldp, a.num_nodes,
-                                          nullptr, lane, gmask, active);
-  if (end > mid)
-    accumulate_range<VEC, L, C, U, WEIGHTED>(acc, a.col, mid, end, a.x + lane * VEC, a.ldx, 0, a.degrees, lane,
-                                             gmask, active);
+  if (mid > begin) {
+    const RowSource src{a.partials + lane * VEC, a.ldp, a.num_nodes, nullptr, 0, 0};
+    accumulate_range<VEC, L, C, U, false, false>(acc, a.col, begin, mid, src, nullptr, lane, gmask, active);
+  }
+  if (end > mid) {
+    const RowSource src{a.x + lane * VEC, a.ldx, 0, nullptr, 0, 0};
+    accumulate_range<VEC, L, C, U, WEIGHTED, false>(acc, a.col, mid, end, src, a.degrees, lane, gmask, active);
+  }
 
   if (dst >= 0) {
     const float scale = row_scale(a, dst, begin == end);
@@ -498,11 +532,9 @@ __global__ void __launch_bounds__(256) gather_rows_ring_kernel(const __grid_cons
 #pragma unroll
         for (int k = 0; k < C; ++k) {
           if (active[k]) {
-            const float4 v = *reinterpret_cast<const float4*>(rp + (size_t)k * (LPR * 16));
-            acc[k][0] = __fadd_rn(acc[k][0], v.x);
-            acc[k][1] = __fadd_rn(acc[k][1], v.y);
-            acc[k][2] = __fadd_rn(acc[k][2], v.z);
-            acc[k][3] = __fadd_rn(acc[k][3], v.w);
+            const float4 v4 = *reinterpret_cast<const float4*>(rp + (size_t)k * (LPR * 16));
+            const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+            acc_add<4>(acc[k], v);
           }
         }
       }
@@ -541,123 +573,6 @@ __global__ void __launch_bounds__(256) gather_rows_ring_kernel(const __grid_cons
 }
 
 // ---------------------------------------------------------------------------------------
-// warp kernel: one warp per work item, items walked in a software-pipelined loop
-// ---------------------------------------------------------------------------------------
-// For plans whose items are short (tens of entries) the lanes kernel is bound by the chain
-// descriptor -> column entries -> rows -> store that every item pays in full: few bytes are in
-// flight while a group waits for its descriptor or its column entries.  Here a resident warp
-// walks items i, i + W, i + 2W, ... (W = warps in the grid; items are sorted by length, so the
-// warps stay balanced) and fetches the descriptor two items ahead and the first 32 column
-// entries one item ahead, so the only latency an item still waits for is that of its rows.
-// R rows are consumed side by side by 32 / R lanes each (rows narrower than a warp's 128 floats),
-// U rows per sub-group are in flight at once, and partial rows and feature rows share one loop
-// (the base pointer is selected per entry: issue slots are free in this regime).
-template <int C, int R, int U, bool WEIGHTED>
-__global__ void __launch_bounds__(256, (C <= 2 ? 4 : 2)) gather_rows_warp_kernel(const __grid_constant__ GatherArgs a) {
-  constexpr int LPR = 32 / R;
-  const int lane = threadIdx.x & 31;
-  const int num_warps = (int)((gridDim.x * blockDim.x) >> 5);
-  int i = (int)((blockIdx.x * blockDim.x + threadIdx.x) >> 5);
-  if (i >= a.num_items) return;
-  const int sr = lane / LPR, vi = lane % LPR;
-  const int nvec = (a.dim + 3) >> 2;
-  const int4* items = reinterpret_cast<const int4*>(a.items);
-  const float* xl = a.x + vi * 4;
-  const float* pl = a.partials + vi * 4;   // only dereferenced for entries >= num_nodes
-
-  bool active[C];
-#pragma unroll
-  for (int k = 0; k < C; ++k) active[k] = (vi + k * LPR) < nvec;
-
-  const int4 none = make_int4(0, 0, 0, 0);
-  int4 d_cur = __ldg(items + i);
-  int4 d_nxt = (i + num_warps < a.num_items) ? __ldg(items + i + num_warps) : none;
-  int cw_cur = (lane < d_cur.y - d_cur.x) ? __ldg(a.col + d_cur.x + lane) : 0;
-
-  for (; i < a.num_items; i += num_warps) {
-    const int begin = d_cur.x, n = d_cur.y - d_cur.x, dst = d_cur.z;
-    // prefetch: the descriptor two items ahead, the first column window one item ahead
-    const int i2 = i + 2 * num_warps;
-    const int4 d_nn = (i2 < a.num_items) ? __ldg(items + i2) : none;
-    const int cw_nxt = (lane < d_nxt.y - d_nxt.x) ? __ldg(a.col + d_nxt.x + lane) : 0;
-
-    float acc[C][4];
-#pragma unroll
-    for (int k = 0; k < C; ++k)
-#pragma unroll
-      for (int t = 0; t < 4; ++t) acc[k][t] = 0.0f;
-
-    for (int w0 = 0; w0 < n; w0 += 32) {   // column windows of 32 entries
-      const int cw = (w0 == 0) ? cw_cur : ((w0 + lane < n) ? __ldg(a.col + begin + w0 + lane) : 0);
-      float wt = 1.0f;
-      if constexpr (WEIGHTED) {
-        if (w0 + lane < n && cw < a.num_nodes) wt = __frsqrt_rn(__ldg(a.degrees + cw));
-      }
-      const int cnt = min(32, n - w0);
-      for (int j0 = 0; j0 < cnt; j0 += R * U) {
-        float v[U][C][4];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int j = j0 + u * R + sr;
-          const int cj = __shfl_sync(0xffffffffu, cw, j & 31);
-          const bool ok = j < cnt;
-          const float* rp = (cj >= a.num_nodes) ? pl + (int64_t)(cj - a.num_nodes) * a.ldp : xl + (int64_t)cj * a.ldx;
-#pragma unroll
-          for (int k = 0; k < C; ++k) {
-            if (ok && active[k]) {
-              load_row_vec<4>(v[u][k], rp + k * (LPR * 4));
-            } else {
-#pragma unroll
-              for (int t = 0; t < 4; ++t) v[u][k][t] = 0.0f;
-            }
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if constexpr (WEIGHTED) {
-            const int j = j0 + u * R + sr;
-            const float wj = __shfl_sync(0xffffffffu, wt, j & 31);
-            if (j < cnt) {   // a weight of an absent entry may be inf: never multiply it in
-#pragma unroll
-              for (int k = 0; k < C; ++k)
-#pragma unroll
-                for (int t = 0; t < 4; ++t) acc[k][t] = __fmaf_rn(wj, v[u][k][t], acc[k][t]);
-            }
-          } else {
-#pragma unroll
-            for (int k = 0; k < C; ++k)
-#pragma unroll
-              for (int t = 0; t < 4; ++t) acc[k][t] = __fadd_rn(acc[k][t], v[u][k][t]);
-          }
-        }
-      }
-    }
-
-    if (R > 1) {  // the R partial sums of the same columns sit LPR lanes apart
-#pragma unroll
-      for (int off = LPR; off < 32; off <<= 1)
-#pragma unroll
-        for (int t = 0; t < 4; ++t) acc[0][t] = __fadd_rn(acc[0][t], __shfl_xor_sync(0xffffffffu, acc[0][t], off));
-    }
-    if (dst >= 0) {
-      if (sr == 0) {
-        const float scale = row_scale(a, dst, n == 0);
-#pragma unroll
-        for (int k = 0; k < C; ++k)
-          if (active[k]) finish_final<4>(a, dst, (vi + k * LPR) * 4, acc[k], scale);
-        if (a.mirror != nullptr && a.mirror_flag_col >= 0 && lane == 0)
-          a.mirror[(int64_t)dst * a.ldm + a.mirror_flag_col] = 1.0f;
-      }
-    } else {
-      finish_segment<4, C>(a, -dst - 1, acc, active, sr == 0, vi, LPR, lane == 0, 0xffffffffu, 0);
-    }
-    d_cur = d_nxt;
-    d_nxt = d_nn;
-    cw_cur = cw_nxt;
-  }
-}
-
-// ---------------------------------------------------------------------------------------
 // tile kernel: rows that neighbouring destinations share are staged once in shared memory
 // ---------------------------------------------------------------------------------------
 // One CTA owns one tile of up to kTileRows short destination rows.  The plan lists the entries
@@ -666,7 +581,8 @@ __global__ void __launch_bounds__(256, (C <= 2 ? 4 : 2)) gather_rows_warp_kernel
 // memory once (weighted by rsqrt(degrees) in GCN mode, so the adds below need no multiply), and
 // each lane group then sums its destination from [slots in shared memory | rows in global
 // memory].  A destination whose neighbours are mostly shared issues one round of global loads
-// instead of four or five, which is what bounds short rows (see gather_rows_warp_kernel).
+// instead of four or five; short rows are bound by those dependent rounds and by instruction issue,
+// not by bandwidth.
 // Upstream stages one part's partial sum per warp in shared memory and fans it out with atomics
 // (reuse_conv_kernel.cu:902-952); here a tile's destinations read every shared row from the
 // same copy and each output row is still stored exactly once.
@@ -728,54 +644,10 @@ __global__ void __launch_bounds__(256, (C <= 2 ? 4 : 2)) gather_tiles_kernel(con
 #pragma unroll
       for (int q = 0; q < 4; ++q) acc[k][q] = 0.0f;
 
-    // global rows first: their loads are in flight while the shared-memory rows are added
-    for (int e = mid; e < end; e += L) {
-      const int mine = e + lane;
-      int c = 0;
-      float w = 1.0f;
-      if (mine < end) {
-        c = __ldg(t.tcol + mine);
-        if constexpr (WEIGHTED) {
-          if (c < a.num_nodes) w = __frsqrt_rn(__ldg(a.degrees + c));
-        }
-      }
-      const int cnt = min(L, end - e);
-      for (int j = 0; j < cnt; j += U) {
-        float v[U][C][4];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int cj = __shfl_sync(gmask, c, (j + u) & (L - 1), L);
-          const bool ok = (j + u) < cnt;
-          const float* rp = (cj >= a.num_nodes) ? a.partials + (int64_t)(cj - a.num_nodes) * a.ldp
-                                                : a.x + (int64_t)cj * a.ldx;
-#pragma unroll
-          for (int k = 0; k < C; ++k) {
-            if (ok && active[k]) {
-              load_row_vec<4>(v[u][k], rp + (lane + k * L) * 4);
-            } else {
-#pragma unroll
-              for (int q = 0; q < 4; ++q) v[u][k][q] = 0.0f;
-            }
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if constexpr (WEIGHTED) {
-            const float wj = __shfl_sync(gmask, w, (j + u) & (L - 1), L);
-            if ((j + u) < cnt) {
-#pragma unroll
-              for (int k = 0; k < C; ++k)
-#pragma unroll
-                for (int q = 0; q < 4; ++q) acc[k][q] = __fmaf_rn(wj, v[u][k][q], acc[k][q]);
-            }
-          } else {
-#pragma unroll
-            for (int k = 0; k < C; ++k)
-#pragma unroll
-              for (int q = 0; q < 4; ++q) acc[k][q] = __fadd_rn(acc[k][q], v[u][k][q]);
-          }
-        }
-      }
+    // rows read from global memory (partial rows and feature rows, selected per entry)
+    if (end > mid) {
+      const RowSource src{a.x + lane * 4, a.ldx, 0, a.partials + lane * 4, a.ldp, a.num_nodes};
+      accumulate_range<4, L, C, U, WEIGHTED, true>(acc, t.tcol, mid, end, src, a.degrees, lane, gmask, active);
     }
     // rows staged in shared memory
     for (int e = begin; e < mid; e += L) {
@@ -787,11 +659,9 @@ __global__ void __launch_bounds__(256, (C <= 2 ? 4 : 2)) gather_tiles_kernel(con
 #pragma unroll
         for (int k = 0; k < C; ++k) {
           if (active[k]) {
-            const float4 v = tile_smem[sj * rowvec + lane + k * L];
-            acc[k][0] = __fadd_rn(acc[k][0], v.x);
-            acc[k][1] = __fadd_rn(acc[k][1], v.y);
-            acc[k][2] = __fadd_rn(acc[k][2], v.z);
-            acc[k][3] = __fadd_rn(acc[k][3], v.w);
+            const float4 v4 = tile_smem[sj * rowvec + lane + k * L];
+            const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+            acc_add<4>(acc[k], v);
           }
         }
       }
@@ -893,13 +763,15 @@ cudaError_t dispatch_width(const GatherArgs& a, cudaStream_t stream) {
   if (nvec <= 8) return launch_one<VEC, 8, 1, 8>(a, stream);
   if (nvec <= 16) return launch_one<VEC, 16, 1, 8>(a, stream);
   const int c = (nvec + 31) / 32;
+  // wide rows (measured on B200, 114.6M-edge graph): 3 vectors per lane run best with two rows in
+  // flight, 4 to 6 with one row in flight and three blocks per SM (width 602: 15.2 vs 18.8 ms)
   switch (c) {
     case 1: return launch_one<VEC, 32, 1, 8>(a, stream);
     case 2: return launch_one<VEC, 32, 2, 4>(a, stream);
     case 3: return launch_one<VEC, 32, 3, 2>(a, stream);
-    case 4: return launch_one<VEC, 32, 4, 2>(a, stream);
-    case 5: return launch_one<VEC, 32, 5, 2>(a, stream);
-    case 6: return launch_one<VEC, 32, 6, 2>(a, stream);
+    case 4: return launch_one<VEC, 32, 4, 1>(a, stream);
+    case 5: return launch_one<VEC, 32, 5, 1>(a, stream);
+    case 6: return launch_one<VEC, 32, 6, 1>(a, stream);
     case 7: case 8: return launch_one<VEC, 32, 8, 1>(a, stream);
     case 9: case 10: return launch_one<VEC, 32, 10, 1>(a, stream);
     case 11: case 12: return launch_one<VEC, 32, 12, 1>(a, stream);
@@ -981,45 +853,6 @@ cudaError_t dispatch_ring(const GatherArgs& a, cudaStream_t stream) {
   }
 }
 
-// ---- warp kernel launch -------------------------------------------------------------------
-template <int C, int R, int U>
-cudaError_t launch_warp_one(const GatherArgs& a, cudaStream_t stream) {
-  const int per_sm = (C <= 2) ? 4 : 2;   // resident blocks of 256 threads (see __launch_bounds__)
-  int sms = 148;
-  int dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess) {
-    static int cached[64] = {0};
-    if (dev >= 0 && dev < 64) {
-      if (cached[dev] == 0 && cudaDeviceGetAttribute(&cached[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-        cached[dev] = 148;
-      sms = cached[dev];
-    }
-  }
-  const int64_t want = ((int64_t)a.num_items + 7) / 8;
-  const unsigned blocks = (unsigned)(want < (int64_t)sms * per_sm ? want : (int64_t)sms * per_sm);
-  if (a.weight_gcn)
-    gather_rows_warp_kernel<C, R, U, true><<<blocks, 256, 0, stream>>>(a);
-  else
-    gather_rows_warp_kernel<C, R, U, false><<<blocks, 256, 0, stream>>>(a);
-  return cudaGetLastError();
-}
-
-cudaError_t dispatch_warp(const GatherArgs& a, cudaStream_t stream) {
-  const int nvec = (a.dim + 3) / 4;
-  if (nvec <= 4) return launch_warp_one<1, 8, 8>(a, stream);
-  if (nvec <= 8) return launch_warp_one<1, 4, 8>(a, stream);
-  if (nvec <= 16) return launch_warp_one<1, 2, 8>(a, stream);
-  switch ((nvec + 31) / 32) {
-    case 1: return launch_warp_one<1, 1, 8>(a, stream);
-    case 2: return launch_warp_one<2, 1, 4>(a, stream);
-    case 3: return launch_warp_one<3, 1, 2>(a, stream);
-    case 4: return launch_warp_one<4, 1, 2>(a, stream);
-    case 5: return launch_warp_one<5, 1, 2>(a, stream);
-    case 6: return launch_warp_one<6, 1, 2>(a, stream);
-    default: return launch_warp_one<8, 1, 1>(a, stream);
-  }
-}
-
 // ---- tile kernel launch -------------------------------------------------------------------
 template <int L, int C, int U>
 cudaError_t launch_tiles_one(const GatherArgs& a, const TileArgs& t, cudaStream_t stream) {
@@ -1044,7 +877,7 @@ cudaError_t launch_tiles_one(const GatherArgs& a, const TileArgs& t, cudaStream_
   return cudaGetLastError();
 }
 
-constexpr int kRingMaxDim = 8 * 32 * 4;  // widest row one ring or warp-kernel launch covers
+constexpr int kRingMaxDim = 8 * 32 * 4;  // widest row one ring launch covers
 
 }  // namespace
 
@@ -1068,20 +901,19 @@ static bool out_allows(const GatherArgs& a, int vec) {
   return a.out == nullptr || (aligned_to(a.out, (size_t)vec * 4) && (a.ldo % vec) == 0);
 }
 
-enum { kKernelLanes = 0, kKernelRing = 1, kKernelWarp = 2 };
+enum { kKernelLanes = 0, kKernelRing = 1 };
 
-// ROF_KERNEL = "ring" | "lanes" | "warp" forces one of the gather kernels wherever the buffers
+// ROF_KERNEL = "ring" | "lanes" forces one of the gather kernels wherever the buffers
 // allow it (experiments, tests); unset: the host policy in GatherArgs::kernel decides
 static int kernel_override() {
   const char* e = std::getenv("ROF_KERNEL");
   if (e == nullptr) return -1;
   if (e[0] == 'r') return kKernelRing;
   if (e[0] == 'l') return kKernelLanes;
-  if (e[0] == 'w') return kKernelWarp;
   return -1;
 }
 
-// The ring and warp kernels need 16-byte aligned rows; the ring kernel does not weight rows.
+// The ring kernel needs 16-byte aligned rows and does not weight rows.
 static int pick_kernel(const GatherArgs& a, int vec) {
   if (vec != 4) return kKernelLanes;
   const int ov = kernel_override();
@@ -1115,7 +947,6 @@ cudaError_t launch_gather(const GatherArgs& a0, cudaStream_t stream, int* launch
     if (a0.dim > tile) a.arrive = nullptr;
     cudaError_t e;
     if (kernel == kKernelRing) e = dispatch_ring(a, stream);
-    else if (kernel == kKernelWarp) e = dispatch_warp(a, stream);
     else e = (vec == 4) ? dispatch_width<4>(a, stream) : (vec == 2) ? dispatch_width<2>(a, stream)
                                                                    : dispatch_width<1>(a, stream);
     if (e != cudaSuccess) return e;

@@ -41,7 +41,6 @@ constexpr int kTileMaxRowEntries = 256;
 constexpr int kTileMaxStage = 64;
 constexpr double kTileMinSaved = 0.25;        // tiles are built when they save at least this share of the global row reads
 constexpr int kTileMaxFloats = 256;           // widest feature row the tile kernel covers
-constexpr double kShortItemEntries = 96.0;    // plans whose items average fewer entries run the warp-per-item kernel
 
 }  // namespace rof
 
@@ -170,7 +169,7 @@ struct GatherArgs {
   int accumulate;   // dst >= 0 rows: out += result instead of out = result
   int out_vec;      // set by launch_gather: `out` rows allow stores as wide as the loads
   int out_padded;   // `out` is library scratch with a padded leading dimension: a ragged last vector is stored whole
-  int kernel;       // host policy: 0 lane groups, 1 shared-memory ring, 2 warp per item (used when the buffers allow it)
+  int kernel;       // host policy: 0 lane groups, 1 shared-memory ring (used when the buffers allow it)
   // split rows finished by their last-arriving segment (all null: split_reduce_kernel does it)
   const int32_t* slot_owner;
   const SplitRow* split;

@@ -1,5 +1,6 @@
-// Splits a plan into per-stage plans for the multi-GPU pipeline: stage k only names feature
-// rows whose owner block has arrived by stage k (see rof_plan_create_stages in rof_b200.h).
+// Splits a plan into per-stage plans: stage k only names feature rows that are readable in stage
+// k — for the multi-GPU pipeline (a peer's block has arrived) and for source tiling (one L2-sized
+// block of source rows at a time); see rof_plan_create_stages* in rof_b200.h.
 #include <algorithm>
 #include <memory>
 
@@ -7,24 +8,12 @@
 
 using namespace rof;
 
-extern "C" int rof_plan_create_stages(const rof_plan* whole, int block_rows, const int32_t* stage_of_block,
-                                      int num_blocks, int num_stages, rof_plan** stages_out, void* stream_) {
-  cudaStream_t stream = (cudaStream_t)stream_;
-  if (!whole || !stage_of_block || !stages_out || block_rows <= 0 || num_blocks <= 0 || num_stages <= 0) {
-    set_error("rof_plan_create_stages: bad argument");
-    return ROF_ERR_BAD_ARGUMENT;
-  }
-  for (int s = 0; s < num_stages; ++s) stages_out[s] = nullptr;
+namespace {
+
+// row_stage[c] = stage in which feature row c becomes readable
+int split_by_row_stage(const rof_plan* whole, const std::vector<int32_t>& row_stage, int num_stages,
+                       rof_plan** stages_out, cudaStream_t stream) {
   const int n = whole->num_nodes;
-  if ((int64_t)block_rows * num_blocks < n) {
-    set_error("rof_plan_create_stages: blocks do not cover every feature row");
-    return ROF_ERR_BAD_ARGUMENT;
-  }
-  for (int b = 0; b < num_blocks; ++b)
-    if (stage_of_block[b] < 0 || stage_of_block[b] >= num_stages) {
-      set_error("rof_plan_create_stages: stage_of_block entry outside [0, num_stages)");
-      return ROF_ERR_BAD_ARGUMENT;
-    }
   const int rows = whole->row_end - whole->row_begin;
   const int G = whole->num_groups;
   try {
@@ -33,8 +22,7 @@ extern "C" int rof_plan_create_stages(const rof_plan* whole, int block_rows, con
     if (rc) return rc;
     const std::vector<int64_t>& row_ptr = whole->h_row_ptr;
     const std::vector<int32_t>& gptr = whole->h_group_ptr;
-    auto stage_of = [&](int32_t c) { return stage_of_block[c / block_rows]; };
-
+    auto stage_of = [&](int32_t c) { return row_stage[(size_t)c]; };
     std::vector<int32_t> gstage((size_t)G, 0), glocal((size_t)G, 0);
     std::vector<HostPlan> hp((size_t)num_stages);
     for (int s = 0; s < num_stages; ++s) {
@@ -88,4 +76,69 @@ extern "C" int rof_plan_create_stages(const rof_plan* whole, int block_rows, con
     return ROF_ERR_NO_MEMORY;
   }
   return ROF_OK;
+}
+
+}  // namespace
+
+extern "C" int rof_plan_create_stages(const rof_plan* whole, int block_rows, const int32_t* stage_of_block,
+                                      int num_blocks, int num_stages, rof_plan** stages_out, void* stream_) {
+  if (!whole || !stage_of_block || !stages_out || block_rows <= 0 || num_blocks <= 0 || num_stages <= 0) {
+    set_error("rof_plan_create_stages: bad argument");
+    return ROF_ERR_BAD_ARGUMENT;
+  }
+  for (int s = 0; s < num_stages; ++s) stages_out[s] = nullptr;
+  const int n = whole->num_nodes;
+  if ((int64_t)block_rows * num_blocks < n) {
+    set_error("rof_plan_create_stages: blocks do not cover every feature row");
+    return ROF_ERR_BAD_ARGUMENT;
+  }
+  for (int b = 0; b < num_blocks; ++b)
+    if (stage_of_block[b] < 0 || stage_of_block[b] >= num_stages) {
+      set_error("rof_plan_create_stages: stage_of_block entry outside [0, num_stages)");
+      return ROF_ERR_BAD_ARGUMENT;
+    }
+  std::vector<int32_t> row_stage;
+  try {
+    row_stage.resize((size_t)n);
+  } catch (const std::bad_alloc&) {
+    set_error("out of host memory while staging the plan");
+    return ROF_ERR_NO_MEMORY;
+  }
+  for (int c = 0; c < n; ++c) row_stage[(size_t)c] = stage_of_block[c / block_rows];
+  return split_by_row_stage(whole, row_stage, num_stages, stages_out, (cudaStream_t)stream_);
+}
+
+extern "C" int rof_plan_create_stages_ranges(const rof_plan* whole, const int32_t* range_bounds,
+                                             const int32_t* stage_of_range, int num_ranges, int num_stages,
+                                             rof_plan** stages_out, void* stream_) {
+  if (!whole || !range_bounds || !stage_of_range || !stages_out || num_ranges <= 0 || num_stages <= 0) {
+    set_error("rof_plan_create_stages_ranges: bad argument");
+    return ROF_ERR_BAD_ARGUMENT;
+  }
+  for (int s = 0; s < num_stages; ++s) stages_out[s] = nullptr;
+  const int n = whole->num_nodes;
+  if (range_bounds[0] != 0 || range_bounds[num_ranges] != n) {
+    set_error("rof_plan_create_stages_ranges: the ranges must cover [0, num_nodes)");
+    return ROF_ERR_BAD_ARGUMENT;
+  }
+  for (int r = 0; r < num_ranges; ++r) {
+    if (range_bounds[r + 1] < range_bounds[r]) {
+      set_error("rof_plan_create_stages_ranges: range bounds must be ascending");
+      return ROF_ERR_BAD_ARGUMENT;
+    }
+    if (stage_of_range[r] < 0 || stage_of_range[r] >= num_stages) {
+      set_error("rof_plan_create_stages_ranges: stage_of_range entry outside [0, num_stages)");
+      return ROF_ERR_BAD_ARGUMENT;
+    }
+  }
+  std::vector<int32_t> row_stage;
+  try {
+    row_stage.resize((size_t)n);
+  } catch (const std::bad_alloc&) {
+    set_error("out of host memory while staging the plan");
+    return ROF_ERR_NO_MEMORY;
+  }
+  for (int r = 0; r < num_ranges; ++r)
+    for (int c = range_bounds[r]; c < range_bounds[r + 1]; ++c) row_stage[(size_t)c] = stage_of_range[r];
+  return split_by_row_stage(whole, row_stage, num_stages, stages_out, (cudaStream_t)stream_);
 }

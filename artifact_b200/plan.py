@@ -199,6 +199,22 @@ class AggregationPlan:
                 self._stream(self.device)))
         return [AggregationPlan(ctypes.c_void_p(h), self.layout + ":stage", self.device, self._keep) for h in handles]
 
+    def stages_by_ranges(self, range_bounds, stage_of_range):
+        """Like `stages` for feature rows owned in ranges of any length
+        (rof_plan_create_stages_ranges): range r = rows [range_bounds[r], range_bounds[r+1]) becomes
+        readable in stage stage_of_range[r]."""
+        rb = np.ascontiguousarray(range_bounds, dtype=np.int32)
+        sr = np.ascontiguousarray(stage_of_range, dtype=np.int32)
+        if rb.size != sr.size + 1:
+            raise ValueError("range_bounds needs one more entry than stage_of_range")
+        num_stages = int(sr.max()) + 1 if sr.size else 1
+        handles = (ctypes.c_void_p * num_stages)()
+        with _device_guard(self.device):
+            _native.check(_native.cuda().rof_plan_create_stages_ranges(
+                self._h, ctypes.c_void_p(rb.ctypes.data), ctypes.c_void_p(sr.ctypes.data), int(sr.size), num_stages,
+                handles, self._stream(self.device)))
+        return [AggregationPlan(ctypes.c_void_p(h), self.layout + ":stage", self.device, self._keep) for h in handles]
+
     # -- inspection --------------------------------------------------------------------
     def export(self):
         i = self.info

@@ -1,49 +1,110 @@
 """Row-block sharding of the aggregation over the GPUs of one node.
 
-Destinations are independent, so rank r owns an equal block of destination rows and a plan
-built for that block only; what the ranks exchange per pass is the feature matrix: every rank
-contributes its block of rows and receives all of them (one all-gather over NCCL / NVLink)
-into a full [N, D] buffer in its own HBM.  Kernels only ever read local memory.
-Upstream is single-GPU (no collective anywhere in its tree); this module is new.
+Destinations are independent, so rank r owns a block of destination rows and a plan built for
+that block only; what the ranks exchange per pass is the feature matrix: every rank contributes
+its block of rows and receives all the others (NCCL over NVLink) into a full [N, D] buffer in its
+own HBM.  Kernels only ever read local memory.  Upstream is single-GPU (no collective anywhere in
+its tree); this module is new.
 """
+import numpy as np
 import torch
 import torch.distributed as dist
 
 
-def row_blocks(num_nodes, world):
-    """-> (block_rows, [(r0, r1)] per rank).  Equal-sized blocks (the last may be short or
-    empty) so that one all_gather_into_tensor moves the whole matrix."""
-    blk = (num_nodes + world - 1) // world if world > 0 else num_nodes
-    return blk, [(min(r * blk, num_nodes), min((r + 1) * blk, num_nodes)) for r in range(world)]
+def row_blocks(num_nodes, world, indptr=None, row_cost=8):
+    """-> (block_rows, [(r0, r1)] per rank).
+
+    Without `indptr`: equal-sized blocks (the last may be short or empty), block_rows = their
+    size, so that one all_gather_into_tensor moves the whole matrix.
+    With `indptr` (the destination CSR's row pointers): contiguous blocks of about equal *work*,
+    work(v) = in-degree(v) + row_cost — on a power-law graph whose hubs sit next to each other equal
+    row counts would give one rank most of the edges.  block_rows is None (blocks differ)."""
+    if world <= 0:
+        return num_nodes, [(0, num_nodes)]
+    if indptr is None:
+        blk = (num_nodes + world - 1) // world
+        return blk, [(min(r * blk, num_nodes), min((r + 1) * blk, num_nodes)) for r in range(world)]
+    ip = np.asarray(indptr, dtype=np.int64)
+    if ip.shape[0] != num_nodes + 1:
+        raise ValueError("indptr must have num_nodes + 1 entries")
+    work = (ip - ip[0]) + row_cost * np.arange(num_nodes + 1, dtype=np.int64)     # cumulative work before row v
+    cuts = [0]
+    for r in range(1, world):
+        cuts.append(int(np.searchsorted(work, work[-1] * r / world, side="left")))
+    cuts.append(num_nodes)
+    cuts = np.maximum.accumulate(np.minimum(cuts, num_nodes))
+    return None, [(int(cuts[r]), int(cuts[r + 1])) for r in range(world)]
 
 
 class ShardedFeatures:
-    """The padded [world*block, D] receive buffer of one feature matrix and its all-gather."""
+    """The receive buffer of one feature matrix and its all-gather.
 
-    def __init__(self, num_nodes, dim, rank, world, device, dtype=torch.float32, group=None):
+    Equal blocks (bounds=None): a padded [world*block, D] buffer filled by one
+    all_gather_into_tensor.  Given `bounds` ([(r0, r1)] per rank, e.g. from row_blocks(...,
+    indptr)): an exact [N, D] buffer whose blocks travel as grouped sends/receives."""
+
+    def __init__(self, num_nodes, dim, rank, world, device, dtype=torch.float32, group=None, bounds=None):
         self.n, self.dim, self.rank, self.world, self.group = num_nodes, dim, rank, world, group
-        self.block, self.blocks = row_blocks(num_nodes, world)
-        self.full = torch.zeros((self.block * world, dim), dtype=dtype, device=device)
+        if bounds is None:
+            self.block, self.blocks = row_blocks(num_nodes, world)
+            self.equal = True
+            rows = self.block * world
+        else:
+            self.blocks = [(int(a), int(b)) for a, b in bounds]
+            if len(self.blocks) != world or self.blocks[0][0] != 0 or self.blocks[-1][1] != num_nodes or any(
+                    self.blocks[i][1] != self.blocks[i + 1][0] for i in range(world - 1)):
+                raise ValueError("bounds must be `world` contiguous blocks covering [0, num_nodes)")
+            self.block, self.equal = None, False
+            rows = num_nodes
+        self.full = torch.zeros((rows, dim), dtype=dtype, device=device)
 
     @property
     def local_rows(self):
         r0, r1 = self.blocks[self.rank]
         return r1 - r0
 
+    def block_view(self, b):
+        """the rows of the buffer that rank b's block occupies (padding rows included for equal blocks)"""
+        if self.equal:
+            return self.full[b * self.block:(b + 1) * self.block]
+        r0, r1 = self.blocks[b]
+        return self.full[r0:r1]
+
     def local_view(self):
-        """this rank's block inside the full buffer (block rows, the tail beyond N is padding)"""
-        return self.full[self.rank * self.block:(self.rank + 1) * self.block]
+        """this rank's block inside the full buffer"""
+        return self.block_view(self.rank)
+
+    def exchange_ops(self, offsets):
+        """grouped point-to-point operations that bring in the blocks of ranks (rank + k) % world, k in
+        `offsets`, and send this rank's block to ranks (rank - k) % world"""
+        ops = []
+        for k in offsets:
+            if k % self.world == 0:
+                continue                             # the rank's own block is already in place
+            src = (self.rank + k) % self.world
+            dst = (self.rank - k) % self.world
+            if self.local_view().numel():
+                ops.append(dist.P2POp(dist.isend, self.local_view(), dst, group=self.group))
+            if self.block_view(src).numel():
+                ops.append(dist.P2POp(dist.irecv, self.block_view(src), src, group=self.group))
+        return ops
 
     def all_gather(self, x_local=None):
-        """x_local: [block, D] (padded) or None to send the rows already in local_view().
-        Returns the full [N, D] matrix (a view without the padding rows)."""
+        """x_local: this rank's block (padded to [block, D] for equal blocks) or None to send the rows
+        already in local_view().  Returns the full [N, D] matrix (a view without padding rows)."""
         src = self.local_view() if x_local is None else x_local
-        if src.shape != (self.block, self.dim):
-            raise RuntimeError(f"local block must be [{self.block}, {self.dim}] (padded), got {tuple(src.shape)}")
+        if tuple(src.shape) != tuple(self.local_view().shape):
+            raise RuntimeError(f"local block must be {tuple(self.local_view().shape)}, got {tuple(src.shape)}")
+        if x_local is not None and x_local.data_ptr() != self.local_view().data_ptr():
+            self.local_view().copy_(x_local)
         if self.world > 1:
-            dist.all_gather_into_tensor(self.full, src.contiguous(), group=self.group)
-        elif x_local is not None:
-            self.full.copy_(src)
+            if self.equal:
+                dist.all_gather_into_tensor(self.full, self.local_view(), group=self.group)
+            else:
+                ops = self.exchange_ops(range(1, self.world))
+                if ops:
+                    for w in dist.batch_isend_irecv(ops):
+                        w.wait()
         return self.full[:self.n]
 
 
@@ -80,64 +141,134 @@ def stage_schedule(world):
     return stages
 
 
+def compute_stages(blocks, rank, schedule, dim, entries_per_row, tile_bytes=64e6, min_entries_per_tile=48):
+    """Cuts every transfer stage into compute stages whose source rows fit L2.
+
+    -> (range_bounds, stage_of_range, transfer_stage_of_compute_stage).  Transfer stage s brings the
+    blocks of ranks (rank + k) % world, k in schedule[s]; when those blocks hold more than
+    `tile_bytes` of features the stage's rows are cut into tiles (contiguous row ranges of about
+    equal size) that are aggregated one after the other, so that the gathers of a tile hit L2
+    (126 MB) — unless a destination would then gather fewer than `min_entries_per_tile` rows per
+    tile, where the extra passes over the output cost more than the misses."""
+    world = len(blocks)
+    n = blocks[-1][1]
+    pieces = []                       # (r0, r1, compute stage)
+    transfer_of = []
+    for s, offs in enumerate(schedule):
+        rng = sorted(blocks[(rank + k) % world] for k in offs)
+        rows = sum(b - a for a, b in rng)
+        tiles = 1
+        if rows > 0:
+            tiles = max(1, int(np.ceil(rows * dim * 4 / tile_bytes)))
+            while tiles > 1 and entries_per_row * (rows / max(n, 1)) / tiles < min_entries_per_tile:
+                tiles -= 1
+        per_tile = int(np.ceil(rows / tiles)) if rows else 0
+        first = len(transfer_of)
+        transfer_of.extend([s] * tiles)
+        done = 0
+        for a, b in rng:
+            while a < b:
+                t = min(done // per_tile, tiles - 1) if per_tile else 0
+                take = min(b - a, (t + 1) * per_tile - done) if t < tiles - 1 else b - a
+                pieces.append((a, a + take, first + t))
+                a += take
+                done += take
+    pieces.sort()
+    bounds, stage_of = [0], []
+    for a, b, k in pieces:
+        if a == b:
+            continue
+        if a != bounds[-1]:
+            raise RuntimeError("blocks do not tile the rows")
+        bounds.append(b)
+        stage_of.append(k)
+    if bounds[-1] != n:
+        raise RuntimeError("blocks do not cover every row")
+    return bounds, stage_of, transfer_of
+
+
 class PipelinedAggregator:
     """All-gather overlapped with aggregation, stage by stage.
 
     Rank r reads its own block in stage 0 and the blocks of ranks (r + k) % world, k in the
     stage's offsets (see stage_schedule), in the later stages.  Each stage's blocks travel as one
     group of paired sends/receives on a side stream (send the own block to rank r-k, receive the
-    block of rank r+k; NVSwitch gives every pair full bandwidth), and the per-stage plans
-    (AggregationPlan.stages) run on the compute stream as soon as their blocks have landed,
-    adding into `out`.  The result equals the whole-plan aggregate up to the order of the fp32
-    adds.  Every kernel reads this GPU's memory only.
+    block of rank r+k; NVSwitch gives every pair full bandwidth), and the per-stage plans run on
+    the compute stream as soon as their blocks have landed, adding into `out`.  A transfer stage
+    whose blocks exceed L2 is aggregated as several compute stages (compute_stages).  The result
+    equals the whole-plan aggregate up to the order of the fp32 adds.  Every kernel reads this
+    GPU's memory only.
     """
 
-    def __init__(self, plan, features: ShardedFeatures, stage_plans=None, schedule=None):
+    def __init__(self, plan, features: ShardedFeatures, stage_plans=None, schedule=None, tile_bytes=64e6,
+                 like=None):
         f = features
         r0, r1 = f.blocks[f.rank]
         if (plan.info["row_begin"], plan.info["row_end"]) != (r0, r1):
             raise RuntimeError("the plan does not cover this rank's row block")
         self.features, self.whole = f, plan
-        self.schedule = schedule or stage_schedule(f.world)
-        stage_of_offset = {k: s for s, ks in enumerate(self.schedule) for k in ks}
-        stage_of_block = [stage_of_offset[(b - f.rank) % f.world] for b in range(f.world)]
-        if stage_plans is not None:
-            self.stage_plans = stage_plans
+        if like is not None:          # a second feature buffer over the same plans (e.g. the gradient's)
+            self.schedule, self.stage_plans, self.transfer_of = like.schedule, like.stage_plans, like.transfer_of
         else:
-            self.stage_plans = plan.stages(f.block, stage_of_block) if f.world > 1 else [plan]
+            self.schedule = schedule or stage_schedule(f.world)
+            if f.world > 1:
+                rows = max(r1 - r0, 1)
+                bounds, stage_of, self.transfer_of = compute_stages(
+                    f.blocks, f.rank, self.schedule, f.dim, plan.info["gather_entries"] / rows, tile_bytes)
+                self.stage_plans = stage_plans or plan.stages_by_ranges(bounds, stage_of)
+            else:
+                self.stage_plans, self.transfer_of = stage_plans or [plan], [0]
         dev = f.full.device
         self.comm_stream = torch.cuda.Stream(dev) if f.world > 1 else None
         self.ready = torch.cuda.Event() if f.world > 1 else None
         self.landed = [torch.cuda.Event() for _ in self.schedule]
         self.launches = 0
 
-    def aggregate(self, x_local, degrees, mode, out):
+    def _transfer(self, cur):
         f = self.features
-        R, r, blk = f.world, f.rank, f.block
-        cur = torch.cuda.current_stream(f.full.device)
-        if x_local is not None:
-            f.local_view().copy_(x_local)
+        self.ready.record(cur)
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(self.ready)
+            for s, offs in enumerate(self.schedule):
+                ops = f.exchange_ops(offs)
+                if ops:
+                    for w in dist.batch_isend_irecv(ops):
+                        w.wait()
+                self.landed[s].record(self.comm_stream)
+
+    def _compute(self, cur, degrees, mode, out, wait=True):
+        f = self.features
         x_full = f.full[:f.n]
-        if R > 1:
-            self.ready.record(cur)
-            with torch.cuda.stream(self.comm_stream):
-                self.comm_stream.wait_event(self.ready)
-                for s in range(len(self.schedule)):
-                    ops = []
-                    for k in self.schedule[s]:
-                        if k == 0:
-                            continue                     # the rank's own block is already in place
-                        src = (r + k) % R
-                        ops.append(dist.P2POp(dist.isend, f.local_view(), (r - k) % R, group=f.group))
-                        ops.append(dist.P2POp(dist.irecv, f.full[src * blk:(src + 1) * blk], src, group=f.group))
-                    if ops:
-                        for w in dist.batch_isend_irecv(ops):
-                            w.wait()
-                    self.landed[s].record(self.comm_stream)
         self.launches = 0
-        for s, p in enumerate(self.stage_plans):
-            if R > 1 and any(k != 0 for k in self.schedule[s]):
+        waited = set()
+        for k, p in enumerate(self.stage_plans):
+            s = self.transfer_of[k]
+            if wait and f.world > 1 and s not in waited and any(o % f.world for o in self.schedule[s]):
                 cur.wait_event(self.landed[s])
-            p.aggregate(x_full, degrees, mode, out=out, accumulate=s > 0)
+                waited.add(s)
+            p.aggregate(x_full, degrees, mode, out=out, accumulate=k > 0)
             self.launches += p.last_launch_count()
         return out
+
+    def aggregate(self, x_local, degrees, mode, out):
+        f = self.features
+        cur = torch.cuda.current_stream(f.full.device)
+        if x_local is not None and x_local.data_ptr() != f.local_view().data_ptr():
+            f.local_view().copy_(x_local)
+        if f.world > 1:
+            self._transfer(cur)
+        return self._compute(cur, degrees, mode, out)
+
+    def transfer_only(self):
+        """the pass's transfers without its kernels (timing breakdown); the current stream waits for them"""
+        f = self.features
+        if f.world <= 1:
+            return
+        cur = torch.cuda.current_stream(f.full.device)
+        self._transfer(cur)
+        for ev in self.landed:
+            cur.wait_event(ev)
+
+    def aggregate_only(self, degrees, mode, out):
+        """the pass's kernels over whatever the buffer holds, without transfers (timing breakdown)"""
+        return self._compute(torch.cuda.current_stream(self.features.full.device), degrees, mode, out, wait=False)

@@ -156,6 +156,16 @@ int rof_plan_export_tiles(const rof_plan* plan, int32_t* tiles, int32_t* titems,
 int rof_plan_create_stages(const rof_plan* whole, int block_rows, const int32_t* stage_of_block,
                            int num_blocks, int num_stages, rof_plan** stages_out, void* stream);
 
+/*
+ * The same split for feature rows owned in ranges of any length (row blocks balanced by edge
+ * count, a peer's block cut into L2-sized tiles): range r covers feature rows
+ * [range_bounds[r], range_bounds[r+1]) and becomes readable in stage stage_of_range[r];
+ * range_bounds has num_ranges + 1 ascending entries from 0 to num_nodes.
+ */
+int rof_plan_create_stages_ranges(const rof_plan* whole, const int32_t* range_bounds,
+                                  const int32_t* stage_of_range, int num_ranges, int num_stages,
+                                  rof_plan** stages_out, void* stream);
+
 /* Bytes of device scratch rof_aggregate() needs for feature width `dim`: the partial-sum
  * rows of phase A plus the segment sums of split rows.  256-byte aligned memory. */
 int64_t rof_plan_workspace_bytes(const rof_plan* plan, int dim);

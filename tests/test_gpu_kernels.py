@@ -34,7 +34,7 @@ def padded(x_np):
     return t
 
 
-@pytest.fixture(params=["lanes", "ring", "warp"])
+@pytest.fixture(params=["lanes", "ring"])
 def kernel(request, monkeypatch):
     monkeypatch.setenv("ROF_KERNEL", request.param)
     return request.param

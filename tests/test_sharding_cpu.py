@@ -84,6 +84,56 @@ def test_row_blocks_cover_and_pad():
             assert all(0 <= r1 - r0 <= blk for r0, r1 in blocks)
 
 
+def test_row_blocks_balanced_by_edges_on_an_unpermuted_power_law_graph():
+    """hubs first (in-degree falls with the node id): equal row counts would give rank 0 most of the
+    edges; blocks cut by in-degree + row cost must be within 15 % of each other"""
+    from artifact_b200.sharding import row_blocks
+    n = 20000
+    deg = np.maximum(1, (20000.0 * (np.arange(n) + 1.0) ** -0.7)).astype(np.int64)
+    indptr = np.concatenate([[0], np.cumsum(deg)])
+    for w in (2, 4, 8):
+        _, eq = row_blocks(n, w)
+        blk, bal = row_blocks(n, w, indptr=indptr)
+        assert blk is None and bal[0][0] == 0 and bal[-1][1] == n
+        assert all(a[1] == b[0] for a, b in zip(bal, bal[1:]))
+        work = lambda blocks: np.array([indptr[b] - indptr[a] + 8 * (b - a) for a, b in blocks], dtype=np.float64)
+        assert work(eq).max() / work(eq).mean() > 1.4              # the problem being solved
+        assert work(bal).max() / work(bal).mean() < 1.15
+    # one rank: everything
+    assert row_blocks(n, 1, indptr=indptr)[1] == [(0, n)]
+
+
+def _unequal_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from artifact_b200.sharding import ShardedFeatures
+    n, dim = 50, 3
+    bounds = [(0, 5), (5, 33), (33, 50)]
+    x = torch.arange(n * dim, dtype=torch.float32).reshape(n, dim)
+    feats = ShardedFeatures(n, dim, rank, world, torch.device("cpu"), bounds=bounds)
+    r0, r1 = bounds[rank]
+    assert tuple(feats.local_view().shape) == (r1 - r0, dim) and feats.full.shape[0] == n
+    full = feats.all_gather(x[r0:r1].clone())
+    q.put((rank, bool(torch.equal(full, x))))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_unequal_blocks_all_gather():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() * 5 + 91) % 2000
+    procs = [ctx.Process(target=_unequal_worker, args=(r, 3, port, q)) for r in range(3)]
+    for p in procs:
+        p.start()
+    got = sorted(q.get(timeout=120) for _ in range(3))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert got == [(0, True), (1, True), (2, True)]
+
+
 def test_stage_schedule_covers_every_peer_once():
     from artifact_b200.sharding import stage_schedule
     for w in (1, 2, 3, 4, 5, 8, 16):
