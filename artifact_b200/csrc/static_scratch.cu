@@ -18,7 +18,10 @@
 // Set-up: the array's name is a host-side stand-in, not a device address, so the address is
 // looked up with cudaGetSymbolAddress — once per device, with that device current, on the
 // first call made on that device.  That first call should therefore be made during start-up,
-// before any stream capture begins.
+// before any stream capture begins — and, because CUDA loads this module lazily, before the host
+// gives the rest of HBM away: the lookup is what makes the driver back the array with memory.
+// The address is cached per device ordinal for the life of the process; it does not survive a
+// cudaDeviceReset().
 #include <mutex>
 
 #include "rof_internal.h"

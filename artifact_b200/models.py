@@ -28,6 +28,7 @@ class ROF_inputInfo:
         self.uniqpart_column_index, self.uniqpart_pointers = uniqpart_column_index, uniqpart_pointers
         self.part2Node_ptr, self.part2Node_col = part2Node_ptr, part2Node_col
         self.dimWorker = 32
+        self.transform_order = "reference"
         self.part_result_cache = None
         self.transposed = None      # optional ROF_inputInfo of the transposed graph (exact backward, directed graphs)
 

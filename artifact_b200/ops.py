@@ -111,6 +111,23 @@ def _aligned_rows(x):
     return scale_rows(x, None, "copy")
 
 
+def aggregate_gcn(kernel_type, info, x):
+    """A_hat x for one of upstream's three kernel types, without a weight: the aggregation step of the
+    seven entry points on its own (used by the layer when it aggregates before it transforms)."""
+    n = x.size(0)
+    if kernel_type == "GNNA":
+        plan = plan_for_parts(n, info.column_index, info.part_pointers, info.part2Node)
+    elif kernel_type == "ROF_v1":
+        plan = plan_for_v1(n, info.column_index, info.part_pointers, info.part2Node, info.part_cache_flagindex,
+                           info.part_pointers_cache, info.column_index_cache)
+    elif kernel_type == "ROF_v2":
+        plan = plan_for_v2(n, info.uniqpart_column_index, info.uniqpart_pointers, info.part2Node_ptr,
+                           info.part2Node_col)
+    else:
+        raise NotImplementedError
+    return plan.aggregate(_aligned_rows(x.contiguous()), info.degrees, "gcn", tiles="auto")
+
+
 def _backward_tail(d_input_prime, X, weight):
     # reuse_conv_kernel.cu:382-383 / 819-820 / 1050-1051
     d_input = torch.mm(d_input_prime, weight.transpose(0, 1))

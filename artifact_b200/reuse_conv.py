@@ -36,6 +36,16 @@ class ROF_GCNConvFunc(torch.autograd.Function):
         # the layer rebinds inputInfo.part_result_cache on every call (one buffer per layer), so the
         # one seen now is the one backward must use (upstream saves it with save_for_backward)
         ctx.cache = info.part_result_cache
+        # Optional, off unless the layer asks for it: A_hat (x W) = (A_hat x) W, so when the input is
+        # narrower than the output the aggregation — the memory-bound step — can run at the input
+        # width, and the backward pass needs no second aggregation for dW (dW = (A_hat x)^T dY).
+        # Upstream always transforms first (reuse_conv_kernel.cu:302, 621, 971).
+        ctx.aggregate_first = (getattr(info, "transform_order", "reference") == "auto"
+                               and x.size(1) < weight.size(1))
+        if ctx.aggregate_first:
+            ax = ROF.aggregate_gcn(kernel_type, info, x)
+            ctx.save_for_backward(ax, weight)
+            return torch.mm(ax, weight)
         ctx.save_for_backward(x, weight)
         ps, dw, wpb = ctx.launch
         if kernel_type == "GNNA":
@@ -59,6 +69,13 @@ class ROF_GCNConvFunc(torch.autograd.Function):
         info = getattr(ctx.info, "transposed", None) or ctx.info
         ps, dw, wpb = ctx.launch
         grad_output = grad_output.contiguous()
+        if ctx.aggregate_first:
+            ax = x                                      # what forward saved is A_hat x
+            d_weight = torch.mm(ax.transpose(0, 1), grad_output)
+            d_input = None
+            if ctx.needs_input_grad[0]:
+                d_input = ROF.aggregate_gcn(ctx.kernel_type, info, torch.mm(grad_output, weight.transpose(0, 1)))
+            return d_input, d_weight, None, None, None
         if ctx.kernel_type == "GNNA":
             d_input, d_weight = ROF.GNNA_backward(grad_output, x, weight, info.column_index, info.degrees,
                                                   info.part_pointers, info.part2Node, ps, dw, wpb)
@@ -85,7 +102,8 @@ class ROF_GCNConv(torch.nn.Module):
     """GCN convolution out = A_hat (x W) + b.  kwargs (reuse_conv.py:102-125): add_self_loops
     (default True, which raises at call time exactly like upstream — pass False), kernel_type
     ('ROF_v1'), reuse_size (rows of part_result_cache = number of reuse groups), dimWorker
-    (0 -> min(out_channels, 32)), weight_initializer ('glorot' | 'uniform' | 'he')."""
+    (0 -> min(out_channels, 32)), weight_initializer ('glorot' | 'uniform' | 'he'); plus one kwarg
+    upstream does not have, transform_order ('reference' | 'auto')."""
 
     def __init__(self, in_channels, out_channels, bias=True, **kwargs):
         super().__init__()
@@ -94,6 +112,9 @@ class ROF_GCNConv(torch.nn.Module):
         self.kernel_type = kwargs.get("kernel_type", "ROF_v1")
         self.reuse_size = kwargs.get("reuse_size", 0)
         self.dimWorker = kwargs.get("dimWorker", 0) or min(out_channels, 32)
+        # "reference": transform, then aggregate, like upstream; "auto": aggregate first when the input
+        # is narrower than the output (same result up to fp32 rounding, fewer bytes gathered)
+        self.transform_order = kwargs.get("transform_order", "reference")
         self.weight = torch.nn.Parameter(torch.empty(in_channels, out_channels))
         if bias:
             self.bias = torch.nn.Parameter(torch.empty(out_channels))
@@ -123,6 +144,7 @@ class ROF_GCNConv(torch.nn.Module):
     def forward(self, x, inputInfo):
         inputInfo.part_result_cache = self.part_result_cache
         inputInfo.dimWorker = self.dimWorker
+        inputInfo.transform_order = self.transform_order
         out = ROF_GCNConvFunc.apply(x, self.weight, inputInfo, self.add_self_loops, self.kernel_type)
         return out if self.bias is None else out + self.bias
 

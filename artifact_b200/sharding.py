@@ -41,7 +41,9 @@ class ShardedFeatures:
 
     Equal blocks (bounds=None): a padded [world*block, D] buffer filled by one
     all_gather_into_tensor.  Given `bounds` ([(r0, r1)] per rank, e.g. from row_blocks(...,
-    indptr)): an exact [N, D] buffer whose blocks travel as grouped sends/receives."""
+    indptr)): an exact [N, D] buffer whose blocks travel as grouped sends/receives.
+    The rows are stored with a stride padded to a multiple of 4 floats (so that the gather kernels
+    use 128-bit loads whatever D is); `full` is the [rows, D] view, and whole padded rows travel."""
 
     def __init__(self, num_nodes, dim, rank, world, device, dtype=torch.float32, group=None, bounds=None):
         self.n, self.dim, self.rank, self.world, self.group = num_nodes, dim, rank, world, group
@@ -56,19 +58,28 @@ class ShardedFeatures:
                 raise ValueError("bounds must be `world` contiguous blocks covering [0, num_nodes)")
             self.block, self.equal = None, False
             rows = num_nodes
-        self.full = torch.zeros((rows, dim), dtype=dtype, device=device)
+        self._store = torch.zeros((rows, (dim + 3) // 4 * 4), dtype=dtype, device=device)
+        self.full = self._store[:, :dim]
 
     @property
     def local_rows(self):
         r0, r1 = self.blocks[self.rank]
         return r1 - r0
 
+    def _block_rows(self, b):
+        if self.equal:
+            return b * self.block, (b + 1) * self.block
+        return self.blocks[b]
+
     def block_view(self, b):
         """the rows of the buffer that rank b's block occupies (padding rows included for equal blocks)"""
-        if self.equal:
-            return self.full[b * self.block:(b + 1) * self.block]
-        r0, r1 = self.blocks[b]
+        r0, r1 = self._block_rows(b)
         return self.full[r0:r1]
+
+    def _block_store(self, b):
+        """the same rows with their padding columns: contiguous, this is what travels"""
+        r0, r1 = self._block_rows(b)
+        return self._store[r0:r1]
 
     def local_view(self):
         """this rank's block inside the full buffer"""
@@ -84,9 +95,9 @@ class ShardedFeatures:
             src = (self.rank + k) % self.world
             dst = (self.rank - k) % self.world
             if self.local_view().numel():
-                ops.append(dist.P2POp(dist.isend, self.local_view(), dst, group=self.group))
+                ops.append(dist.P2POp(dist.isend, self._block_store(self.rank), dst, group=self.group))
             if self.block_view(src).numel():
-                ops.append(dist.P2POp(dist.irecv, self.block_view(src), src, group=self.group))
+                ops.append(dist.P2POp(dist.irecv, self._block_store(src), src, group=self.group))
         return ops
 
     def all_gather(self, x_local=None):
@@ -99,7 +110,7 @@ class ShardedFeatures:
             self.local_view().copy_(x_local)
         if self.world > 1:
             if self.equal:
-                dist.all_gather_into_tensor(self.full, self.local_view(), group=self.group)
+                dist.all_gather_into_tensor(self._store, self._block_store(self.rank), group=self.group)
             else:
                 ops = self.exchange_ops(range(1, self.world))
                 if ops:

@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the reuse aggregation hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c4|c5] [--dim D]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c2|c3|c4|c5] [--dim D]
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
     python bench.py --impl reference ...      # CPU plain aggregation on the host cores
 
@@ -11,12 +11,15 @@ seeded synthetic graph of the workload, through the reuse plan built from the RO
 `value` is edges/s with the ORIGINAL edge count (reuse shows up as more edges per second),
 inputs resident in HBM; `e2e` is the same step through the public API with pinned-host inputs
 and outputs, copies inside the timed region.  With N > 1 the destination rows are cut into N
-equal blocks; every pass moves the feature blocks between the ranks over NCCL (staged
+blocks of equal work; every pass moves the feature blocks between the ranks over NCCL (staged
 send/receive groups overlapped with the per-stage aggregation, or one all-gather with
 --no-pipeline) and the same total work is divided (strong scaling).  On one GPU a feature matrix
-larger than L2 is walked in source tiles (--tiles).  Prints ONE JSON line on rank 0.
+larger than L2 is walked in source tiles (--tiles).  After the timed region every rank
+recomputes a sample of its output rows in fp64 on the host (`check`); a failed check makes the
+run exit non-zero.  Prints ONE JSON line on rank 0.
 """
 import argparse
+import glob
 import json
 import os
 import subprocess
@@ -30,18 +33,21 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: (config function key, default feature width, part_size, mode)
-    "c2": ("c2", 256, 2, "sum"),
-    "c4": ("c4", 256, 2, "gcn"),
-    "c5": ("c5", 64, 2, "sum"),
+    # name: (default feature width, part_size, mode)
+    "c2": (256, 2, "sum"),
+    "c3": (128, 2, "sum"),
+    "c4": (256, 2, "gcn"),
+    "c5": (64, 2, "sum"),
 }
+CACHE_VERSION = 2          # bump when the graph generators or the search change what they produce
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one phase-B launch, from the ncu captures
-# summarised in profiles/gather_rows_<workload>_d<D>_<mode>.md (captured once per kernel change)
-NCU_DRAM_BYTES_PER_LAUNCH = {
-    "c2:D256:sum": 5.13e9,     # one pass = 4 source tiles x 1.28 GB (untiled: 25.03 GB)
+# dram__bytes_read.sum + dram__bytes_write.sum of one pass of the dominant kernel, from committed
+# ncu captures (one per kernel change); None where no capture exists
+NCU_DRAM_BYTES_PER_PASS = {
+    "c2:D256:sum": 5.13e9,     # 4 source tiles x 1.28 GB (untiled: 25.03 GB)
     "c2:D64:sum": 1.44e9,
+    "c5:D64:sum": 2.03e9,
 }
 
 
@@ -107,7 +113,7 @@ class ClockSampler:
 
 def build_graph(name, scale):
     from artifact_b200 import graphs
-    return graphs.CONFIGS[WORKLOADS[name][0]](scale)
+    return graphs.CONFIGS[name](scale)
 
 
 # --------------------------------------------------------------------------------------------
@@ -149,11 +155,42 @@ def cpu_plain(g, dim, mode, seconds_budget, steps=1, warmup=0, threads=0):
                       f"{steps} step(s)", "ms_per_step": ms}
 
 
+def cpu_torch_sparse(g, dim, seconds_budget=6.0):
+    """The same reuse-free sum as torch's own CSR x dense product on the host cores: the stand-in for
+    the PyG / torch_sparse CPU path the benchmark names (not installable here, no network)."""
+    import torch
+    from artifact_b200 import _native
+    cores = _native.host_cores()
+    torch.set_num_threads(cores)
+    n, ip = g.num_nodes, g.indptr_dst
+    r1 = int(min(n, max(1, np.searchsorted(ip, max(1, g.num_edges // 50)))))
+    x = torch.randn((n, dim))
+
+    def make(rows):
+        e = int(ip[rows])
+        return torch.sparse_csr_tensor(torch.from_numpy(ip[:rows + 1].astype(np.int64)),
+                                       torch.from_numpy(g.indices_src[:e].astype(np.int64)), torch.ones(e),
+                                       size=(rows, n)), e
+
+    a, e = make(r1)
+    t = time.perf_counter(); a @ x; dt = max(time.perf_counter() - t, 1e-6)
+    want = int(min(g.num_edges, max(e, e * (seconds_budget / 4.0) / dt)))
+    r1 = int(min(n, max(1, np.searchsorted(ip, want))))
+    a, e = make(r1)
+    a @ x
+    times = []
+    for _ in range(3):
+        t = time.perf_counter(); a @ x; times.append(time.perf_counter() - t)
+    s = float(np.mean(times))
+    return {"value": e / s, "unit": "edges/s", "cores": int(cores), "kind": "torch.sparse CSR x dense (forward pass)",
+            "sample": f"rows [0,{r1}) = {e} of {g.num_edges} edges, D={dim}, 3 passes"}
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    wl, dim, ps, mode = args.workload, args.dim, args.part_size, args.mode
+    wl, dim, mode = args.workload, args.dim, args.mode
     g = build_graph(wl, args.scale)
     cb = cpu_plain(g, dim, mode, seconds_budget=120.0, steps=args.steps, warmup=args.warmup)
     line = {
@@ -170,15 +207,38 @@ def run_reference(args):
 
 _V2_KEYS = ("uniqpart_column_index", "uniqpart_pointers", "part2Node_ptr", "part2Node_col", "picked_fanout",
             "part2Node")
+_V1_KEYS = ("column_index", "part_pointers", "part_cache_flagindex", "part_pointers_cache", "column_index_cache")
+
+
+class _Lazy(dict):
+    """layout arrays read from the cache file on first use (the ROF_v1 arrays are only needed by the
+    upstream-kernel comparison)"""
+
+    def __init__(self, z, keys):
+        super().__init__()
+        self._z, self._keys = z, set(keys)
+
+    def __missing__(self, k):
+        if k not in self._keys:
+            raise KeyError(k)
+        v = self._z[k]
+        self[k] = v
+        return v
+
+    def __contains__(self, k):
+        return dict.__contains__(self, k) or k in self._keys
 
 
 def prepare_workload(args, rank, world):
-    """-> (graph, layouts needed for the ROF_v2 plan, seconds for graph, seconds for search)"""
-    from artifact_b200 import graphs, search
+    """-> (graph, layouts, seconds for graph, seconds for search).  Everything is seeded, so every
+    rank could compute it; to keep the host cores for one search, rank 0 computes and leaves the
+    arrays in a cache directory that the other ranks (and the next invocation on the same box) load."""
+    from artifact_b200 import graphs
     cache_dir = os.environ.get("ROF_CACHE_DIR", "/tmp/rof_b200_cache")
-    path = os.path.join(cache_dir, f"{args.workload}_scale{args.scale}_ps{args.part_size}.npz")
+    path = os.path.join(cache_dir, f"{args.workload}_scale{args.scale}_ps{args.part_size}_v{CACHE_VERSION}.npz")
+
     def compute():
-        from artifact_b200 import _native
+        from artifact_b200 import _native, search
         _native.use_all_host_cores()          # torchrun exports OMP_NUM_THREADS=1; only rank 0 computes
         t0 = time.time()
         g = build_graph(args.workload, args.scale)
@@ -191,13 +251,11 @@ def prepare_workload(args, rank, world):
         z = np.load(path)
         g = graphs.Graph(args.workload, int(z["num_nodes"]), z["indptr_dst"], z["indices_src"], None, None,
                          bool(z["symmetric"]), 0)
-        L = {k: z[k] for k in _V2_KEYS}
+        L = _Lazy(z, _V2_KEYS + _V1_KEYS)
         L["part_size"] = args.part_size
         L["original_column_index"] = g.indices_src
         return g, L
 
-    # rank 0 makes sure the cache file exists (loading it, or computing and saving); every rank
-    # then passes the same barrier, and the other ranks load the file
     result = None
     if rank == 0:
         if os.path.exists(path):
@@ -214,7 +272,8 @@ def prepare_workload(args, rank, world):
                 os.makedirs(cache_dir, exist_ok=True)
                 tmp = path + f".tmp{os.getpid()}.npz"
                 np.savez(tmp, num_nodes=np.int64(g.num_nodes), symmetric=np.int64(g.symmetric),
-                         indptr_dst=g.indptr_dst, indices_src=g.indices_src, **{k: L[k] for k in _V2_KEYS})
+                         indptr_dst=g.indptr_dst, indices_src=g.indices_src,
+                         **{k: L[k] for k in _V2_KEYS + _V1_KEYS})
                 os.replace(tmp, path)
             except Exception:
                 pass
@@ -236,12 +295,345 @@ def workload_config(args, g, ratios):
                      f"D={args.dim}, {args.mode} aggregation, forward+backward pass per step",
          "part_size": args.part_size, "layout": "ROF_v2", "scale": args.scale, "source_tiles": args.tiles,
          "l2": "feature matrix and index arrays together exceed L2 (126 MB); no flush between iterations",
-         "parallelism": (f"row-block x{args.gpus}, " + ("all-gather rounds overlapped with staged aggregation"
-                                                        if args.pipeline else "all-gather then aggregate"))
+         "parallelism": (f"row-block x{args.gpus} (blocks of equal work), "
+                         + ("staged send/receive rounds overlapped with per-stage aggregation"
+                            if args.pipeline else "all-gather then aggregate"))
          if args.gpus > 1 else "single GPU"}
     if ratios is not None:
         c["reuse"] = ratios
     return c
+
+
+# --------------------------------------------------------------------------------------------
+# one workload on this rank: plans, buffers, timing, check
+# --------------------------------------------------------------------------------------------
+class Job:
+    def __init__(self, ns, rank, world, dev, want_plain):
+        import torch
+        from artifact_b200 import search
+        from artifact_b200.plan import AggregationPlan
+        from artifact_b200.sharding import PipelinedAggregator, ShardedFeatures, row_blocks
+        self.torch, self.ns, self.rank, self.world, self.dev = torch, ns, rank, world, dev
+        self.g, self.L, self.t_graph, self.t_search = prepare_workload(ns, rank, world)
+        g, L = self.g, self.L
+        self.n, self.E, self.D, self.mode = g.num_nodes, g.num_edges, ns.dim, ns.mode
+        self.ratios = search.reuse_ratios(L)
+        n, D = self.n, self.D
+        pipelined = world > 1 and ns.pipeline
+        # blocks of equal work for the staged pipeline (its transfers are point to point and take any
+        # block size); the one-collective path needs equal row counts
+        self.blk, self.blocks = row_blocks(n, world, indptr=g.indptr_dst if pipelined else None)
+        self.r0, self.r1 = self.blocks[rank]
+        t0 = time.time()
+        i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32))
+        v2 = [i32(L[k]) for k in ("uniqpart_column_index", "uniqpart_pointers", "part2Node_ptr", "part2Node_col")]
+        self.plan = AggregationPlan.from_v2(n, *v2, rows=(self.r0, self.r1), device=dev)
+        del v2
+        self.plain = None
+        if want_plain:
+            self.plain = AggregationPlan.from_parts(n, i32(g.indices_src), i32(g.indptr_dst), i32(np.arange(n)),
+                                                    rows=(self.r0, self.r1), device=dev)
+        self.deg = torch.from_numpy(np.maximum(g.degrees_f32(), 1.0)).to(dev)
+        gen = torch.Generator(device=dev); gen.manual_seed(1234)
+        bounds = self.blocks if pipelined else None
+        self.feat_x = ShardedFeatures(n, D, rank, world, dev, bounds=bounds)
+        self.feat_g = ShardedFeatures(n, D, rank, world, dev, bounds=bounds)
+        # every rank draws the same full matrices, so the all-gathered content is what it already holds
+        self.feat_x.full.normal_(generator=gen); self.feat_g.full.normal_(generator=gen)
+        rows = self.r1 - self.r0
+        self.out_f = torch.empty((rows, D), device=dev)
+        self.out_b = torch.empty((rows, D), device=dev)
+        if world == 1 or not ns.pipeline:
+            self.tiles = self.plan.auto_tiles(D) if ns.tiles == "auto" else int(ns.tiles)
+        else:
+            self.tiles = 1                 # the pipeline's stages are already source-blocked
+        self.pipes = {}
+        if pipelined:
+            sched = [[int(k) for k in st.split(",")] for st in ns.schedule.split("|")] if ns.schedule else None
+            px = PipelinedAggregator(self.plan, self.feat_x, schedule=sched)
+            self.pipes = {id(self.feat_x): px, id(self.feat_g): PipelinedAggregator(self.plan, self.feat_g, like=px)}
+            self.stage_info = {"transfer_stages": px.schedule, "compute_stages": len(px.stage_plans)}
+        self.t_plan = time.time() - t0
+        self.launches = 0
+        self.gather_events = []
+
+    def ev(self):
+        return self.torch.cuda.Event(enable_timing=True)
+
+    def one_pass(self, p, feat, out, timed_gather=False):
+        if self.pipes and p is self.plan:       # transfers overlapped with the per-stage aggregation
+            pipe = self.pipes[id(feat)]
+            pipe.aggregate(None, self.deg, self.mode, out)
+            self.launches += pipe.launches
+            return
+        xs = feat.all_gather(None) if self.world > 1 else feat.full[:self.n]
+        p.aggregate(xs, self.deg, self.mode, out=out, tiles=self.tiles,
+                    gather_events=self.gather_events if timed_gather else None)
+        self.launches += p.last_launch_count()
+
+    def step(self, p, timed_gather=False):
+        self.one_pass(p, self.feat_x, self.out_f, timed_gather)
+        self.one_pass(p, self.feat_g, self.out_b, timed_gather)
+
+    def _bracket(self, fn, steps, warmup):
+        """`fn` x steps timed with events between barriers; max over ranks; -> (ms per call, wall t0, t1)"""
+        torch = self.torch
+        import torch.distributed as dist
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        s, e = self.ev(), self.ev()
+        w0 = time.time()
+        s.record()
+        for _ in range(steps):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        if self.world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        w1 = time.time()
+        ms = torch.tensor([s.elapsed_time(e)], device=self.dev)
+        if self.world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item()) / steps, w0, w1
+
+    def timed(self, p, steps, warmup, timed_gather=False):
+        for _ in range(warmup):
+            self.step(p)
+        self.launches = 0
+        self.gather_events = []
+        return self._bracket(lambda: self.step(p, timed_gather), steps, 0)
+
+    # ---- correctness: a sample of this rank's output rows recomputed on the host in fp64 ----
+    def check(self, rows_wanted=48):
+        torch = self.torch
+        import torch.distributed as dist
+        g, r0, r1 = self.g, self.r0, self.r1
+        ip = g.indptr_dst
+        lens = np.diff(ip[r0:r1 + 1])
+        worst, count = 0.0, 0
+        if r1 > r0:
+            order = np.argsort(lens, kind="stable")
+            nonempty = order[lens[order] > 0]
+            rng = np.random.default_rng(77 + self.rank)
+            pick = set(order[-3:].tolist()) | set(nonempty[:3].tolist()) | set(order[:1].tolist())
+            pick |= set(rng.integers(0, r1 - r0, size=max(0, rows_wanted - len(pick))).tolist())
+            deg64 = np.maximum(g.degrees_f32(), 1.0).astype(np.float64)
+            for feat, out in ((self.feat_x, self.out_f), (self.feat_g, self.out_b)):
+                full = feat.full[:self.n]
+                for lr in sorted(pick):
+                    v = r0 + lr
+                    idx = g.indices_src[ip[v]:ip[v + 1]].astype(np.int64)
+                    xs = full[torch.from_numpy(idx).to(self.dev)].cpu().numpy().astype(np.float64)
+                    if self.mode == "gcn":
+                        want = (xs / np.sqrt(deg64[idx])[:, None]).sum(0) / np.sqrt(deg64[v])
+                    elif self.mode == "mean":
+                        want = xs.sum(0) / deg64[v] if len(idx) else xs.sum(0)
+                    else:
+                        want = xs.sum(0)
+                    got = out[lr].cpu().numpy().astype(np.float64)
+                    tol = 1e-6 + 1e-5 * max(np.abs(want).max(), 1e-30)
+                    err = np.abs(got - want).max() / tol if np.isfinite(got).all() else float("inf")
+                    worst = max(worst, float(err))
+                    count += 1
+        t = torch.tensor([worst, float(count)], device=self.dev, dtype=torch.float64)
+        if self.world > 1:
+            w = t[:1].clone(); c = t[1:].clone()
+            dist.all_reduce(w, op=dist.ReduceOp.MAX)
+            dist.all_reduce(c, op=dist.ReduceOp.SUM)
+            worst, count = float(w.item()), float(c.item())
+        return {"rows": int(count), "max_scaled_err": worst, "ok": bool(worst <= 1.0),
+                "what": "sampled output rows of every rank (3 longest, 3 shortest, random) of the forward and the "
+                        "backward pass, recomputed from the CSR in fp64 on the host; error in units of the "
+                        "tolerance 1e-6 + 1e-5 x row maximum"}
+
+    # ---- the dominant kernel: phase B of this rank's block ------------------------------------
+    def roofline(self, hbm_peak, peak_kind):
+        torch = self.torch
+        ge = self.gather_events
+        if not ge:             # pipelined run: time this rank's whole-block gather on its own
+            xs = self.feat_x.full[:self.n]
+            for i in range(8):
+                e0, e1 = self.ev(), self.ev()
+                e0.record(); self.plan.aggregate(xs, self.deg, self.mode, out=self.out_f, phases=2); e1.record()
+                if i >= 3:
+                    ge.append((e0, e1))
+            torch.cuda.synchronize()
+        per_pass = max(self.tiles, 1) if not self.pipes else 1
+        gms = float(np.sum([a.elapsed_time(b) for a, b in ge])) / (len(ge) / per_pass)
+        info, rows, D = self.plan.info, self.r1 - self.r0, self.D
+        gather_bytes = 4.0 * D * (info["gather_entries"] + rows) + 4.0 * info["gather_entries"] + 4.0 * (rows + 1)
+        if self.mode == "gcn":
+            gather_bytes += 4.0 * (info["gather_entries"] - info["partial_entries"])
+        achieved = gather_bytes / (gms / 1e3) / 1e9
+        kernel = "gather_tiles_kernel + gather_rows_kernel (phase B)" if info["num_tiles"] else "gather_rows_kernel (phase B)"
+        r = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+             "traffic": None, "kernel": kernel, "ms_per_launch": gms, "launches_per_pass": per_pass,
+             "algorithmic_bytes_per_launch": gather_bytes, "peak_kind": f"{peak_kind} copy bandwidth",
+             "note": "algorithmic bytes = (gathered rows + written rows) x 4D + 4 per index; rows gathered more than "
+                     "once are re-read from L2, so achieved can exceed the DRAM peak: roofline_l2 is the bound then"}
+        ns = self.ns
+        if self.world == 1 and ns.scale == 1.0 and ns.part_size == WORKLOADS[ns.workload][1]:
+            r["traffic"] = NCU_DRAM_BYTES_PER_PASS.get(f"{ns.workload}:D{D}:{self.mode}")
+        return r
+
+    # ---- N > 1: where a pass's time goes ------------------------------------------------------
+    def breakdown(self, iters=10):
+        if not self.pipes:
+            return None
+        px, pg = self.pipes[id(self.feat_x)], self.pipes[id(self.feat_g)]
+        t_all, _, _ = self._bracket(lambda: (px.aggregate(None, self.deg, self.mode, self.out_f),
+                                             pg.aggregate(None, self.deg, self.mode, self.out_b)), iters, 2)
+        t_tr, _, _ = self._bracket(lambda: (px.transfer_only(), pg.transfer_only()), iters, 2)
+        t_ag, _, _ = self._bracket(lambda: (px.aggregate_only(self.deg, self.mode, self.out_f),
+                                            pg.aggregate_only(self.deg, self.mode, self.out_b)), iters, 2)
+        recv = sum((b - a) for i, (a, b) in enumerate(self.blocks) if i != self.rank) * self.D * 4
+        return {"overlapped_ms": round(t_all, 4), "transfer_only_ms": round(t_tr, 4), "aggregate_only_ms": round(t_ag, 4),
+                "received_bytes_per_pass": int(recv),
+                "receive_GBs_transfer_only": round(2 * recv / (t_tr / 1e3) / 1e9, 1) if t_tr > 0 else None,
+                "note": "per step (two passes), max over ranks: the staged send/receive schedule without kernels, the "
+                        "per-stage kernels without transfers, and both together"}
+
+    # ---- end to end: pinned host buffers in and out, copies inside the timed region -----------
+    def e2e(self, steps):
+        torch = self.torch
+        from artifact_b200.streaming import HostStreamedAggregator
+        rows, D, n = self.r1 - self.r0, self.D, self.n
+        up_rows = self.feat_x.local_view().shape[0]
+        h_x = torch.empty((up_rows, D), pin_memory=True); h_x.copy_(self.feat_x.local_view())
+        h_g = torch.empty((up_rows, D), pin_memory=True); h_g.copy_(self.feat_g.local_view())
+        h_of = torch.empty((rows, D), pin_memory=True)
+        h_ob = torch.empty((rows, D), pin_memory=True)
+        # two device slots: slot 0 is the benchmark's x buffers, slot 1 its gradient buffers; the forward
+        # pass of a step goes through one, the backward pass through the other, so that the upload of a
+        # pass overlaps the kernels of the pass before it and the download those of the pass after it
+        slots = []
+        for feat, out in ((self.feat_x, self.out_f), (self.feat_g, self.out_b)):
+            slots.append((feat.local_view(), out,
+                          (lambda feat=feat, out=out: self.one_pass(self.plan, feat, out))))
+        hs = HostStreamedAggregator(slots, self.dev)
+
+        def e2e_step(aggregate=True):
+            hs.submit(h_x, h_of, aggregate)
+            hs.submit(h_g, h_ob, aggregate)
+
+        def run(aggregate):
+            def fn():
+                e2e_step(aggregate)
+            # the last step's downloads must have landed before the end event
+            def fn_all():
+                for _ in range(steps):
+                    fn()
+                hs.join()
+            ms, _, _ = self._bracket(fn_all, 1, 1)
+            return ms / steps
+
+        ms_e2e = run(True)
+        ms_copy = run(False)
+        # restore the device-resident inputs the other measurements use
+        self.feat_x.local_view().copy_(h_x); self.feat_g.local_view().copy_(h_g)
+        torch.cuda.synchronize()
+        return {"value": 2.0 * self.E / (ms_e2e / 1e3), "unit": "edges/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": 2 * n * D * 4, "d2h_bytes_per_step": 2 * n * D * 4,
+                "copy_only_ms": ms_copy,
+                "note": "features and gradients copied from pinned host memory, both results copied back, every step "
+                        "(artifact_b200.streaming.HostStreamedAggregator: uploads and downloads on their own streams, "
+                        "double-buffered on the device); copy_only_ms is the same schedule without the kernels; bytes "
+                        "are summed over the ranks; the graph plan stays resident like upstream's inputInfo tensors"}
+
+    def release(self):
+        for k in ("plan", "plain", "pipes", "feat_x", "feat_g", "out_f", "out_b", "deg", "L", "g"):
+            setattr(self, k, None)
+        self.torch.cuda.empty_cache()
+
+
+# --------------------------------------------------------------------------------------------
+# upstream's own CUDA kernels on the same GPU and graph (single GPU; skipped when not built)
+# --------------------------------------------------------------------------------------------
+def upstream_gpu(job, dims=(128, 256), warmup=5, iters=10):
+    import importlib.util
+    import torch
+    so = glob.glob(os.path.join(ROOT, "oracle", "_ref", "ROF_ref*.so"))
+    if not so:
+        return {"skipped": "upstream CUDA extension not built (oracle/_ref/ROF_ref*.so absent)"}
+    from artifact_b200 import ops
+    spec = importlib.util.spec_from_file_location("ROF_ref", so[0])
+    up = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(up)
+    g, L, dev, n = job.g, job.L, job.dev, job.n
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+    ci, pp, p2n = t(g.indices_src), t(L["part_pointers"]), t(L["part2Node"])
+    v1 = [t(L[k]) for k in ("column_index", "part_pointers", "part2Node", "part_cache_flagindex",
+                            "part_pointers_cache", "column_index_cache")]
+    v2 = [t(L[k]) for k in ("uniqpart_column_index", "uniqpart_pointers", "part2Node_ptr", "part2Node_col")]
+    G = len(L["part_pointers_cache"]) - 1
+    if G < 1:
+        return {"skipped": "no reuse group: upstream's ROF_v1 path exits the process then"}
+    ps, wpb, f_in = int(L["part_size"]), 4, 64
+    X = torch.randn((n, f_in), device=dev)
+    res = {"method": f"{warmup} warm-up + {iters} timed calls, CUDA events around each call with a device "
+                     "synchronise, X.W time subtracted (ROF_evaluation/cuda/small-main.py:360-390, 434-478); "
+                     "forward aggregation of the whole graph", "f_in": f_in, "rows": []}
+
+    def timed(fn):
+        ms = []
+        for i in range(warmup + iters):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record(); fn(); e.record(); torch.cuda.synchronize()
+            if i >= warmup:
+                ms.append(s.elapsed_time(e))
+        return float(np.mean(ms))
+
+    for D in dims:
+        W = torch.randn((f_in, D), device=dev)
+        cache = torch.zeros((G, D + 1), device=dev)
+        dw = min(D, 32)
+        mm = timed(lambda: torch.mm(X, W))
+        row = {"D": D, "mm_ms": round(mm, 4)}
+        for name, mod in (("upstream", up), ("new", ops)):
+            row[name] = {
+                "GNNA": round(timed(lambda: mod.GNNA_forward(X, W, ci, job.deg, pp, p2n, ps, dw, wpb)) - mm, 4),
+                "ROF_v1": round(timed(lambda: mod.reuse_forward_v1(X, W, v1[0], job.deg, v1[1], v1[2], ps, dw, wpb, cache,
+                                                                   v1[3], v1[4], v1[5])) - mm, 4),
+                "ROF_v2": round(timed(lambda: mod.reuse_forward_v2(X, W, v2[0], job.deg, v2[1], v2[2], v2[3], ps, dw,
+                                                                   wpb)) - mm, 4),
+            }
+        row["speedup"] = {k: round(row["upstream"][k] / max(row["new"][k], 1e-6), 1) for k in row["new"]}
+        res["rows"].append(row)
+        del W, cache
+    ops.clear_plan_cache()
+    return res
+
+
+def side_config(name, args, rank, world, dev, steps):
+    """ms per step and check of another benchmark configuration, with the same machinery"""
+    d, ps, mode = WORKLOADS[name]
+    ns = argparse.Namespace(**vars(args))
+    ns.workload, ns.dim, ns.part_size, ns.mode, ns.tiles, ns.schedule = name, d, ps, mode, "auto", ""
+    job = Job(ns, rank, world, dev, want_plain=(world == 1))
+    try:
+        ms, _, _ = job.timed(job.plan, steps, 3)
+        out = {"workload": workload_config(ns, job.g, job.ratios)["workload"], "ms_per_step": round(ms, 4),
+               "edges_per_s": 2.0 * job.E / (ms / 1e3), "check": job.check(24), "n_gpus": world,
+               "tile_kernel": {"tiles": job.plan.info["num_tiles"],
+                               "entries_from_shared_memory": job.plan.info["tile_shared_entries"]}}
+        if job.plain is not None:
+            mp_, _, _ = job.timed(job.plain, max(3, steps // 2), 3)
+            out["plain_ms_per_step"] = round(mp_, 4)
+            out["reuse_speedup"] = round(mp_ / ms, 4)
+        bd = job.breakdown(5)
+        if bd:
+            out["breakdown"] = bd
+            out["stages"] = job.stage_info
+        out["setup_s"] = {"graph": round(job.t_graph, 2), "reuse_search": round(job.t_search, 2),
+                          "plans": round(job.t_plan, 2)}
+        return out
+    finally:
+        job.release()
 
 
 # --------------------------------------------------------------------------------------------
@@ -262,23 +654,24 @@ def main():
     ap.add_argument("--tiles", default="auto", help="source tiles per pass on one GPU: auto or an integer")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--only-kernel", action="store_true", help="skip sweep, CPU baseline and e2e (profiling)")
+    ap.add_argument("--no-configs", action="store_true", help="skip the other benchmark configurations (c4, c5, c3)")
+    ap.add_argument("--no-upstream", action="store_true", help="skip timing upstream's own CUDA kernels")
+    ap.add_argument("--only-kernel", action="store_true", help="only the timed steps (profiling)")
     args = ap.parse_args()
-    _, d_dim, d_ps, d_mode = WORKLOADS[args.workload]
+    d_dim, d_ps, d_mode = WORKLOADS[args.workload]
     args.dim = args.dim or d_dim
     args.part_size = args.part_size or d_ps
     args.mode = args.mode or d_mode
     args.warmup = max(args.warmup, 3)
     if args.only_kernel:
-        args.no_sweep = args.no_cpu = True
+        args.no_sweep = args.no_cpu = args.no_configs = args.no_upstream = True
 
     if args.impl == "reference":
         return run_reference(args)
 
     import torch
     import torch.distributed as dist
-    from artifact_b200 import search
-    from artifact_b200.plan import AggregationPlan
+    from artifact_b200.plan import probe_read_gbs
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the aggregation path has no CPU fallback")
@@ -291,207 +684,62 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
     hbm_peak, peak_kind = load_peaks()
 
-    # ---- workload: graph -> reuse search -> plans ------------------------------------------
-    # Everything is seeded, so every rank could compute it; to keep the host cores for one
-    # search, rank 0 computes and leaves the arrays in a cache directory the other ranks (and
-    # the next invocation on the same box) load.
-    g, L, t_graph, t_search = prepare_workload(args, rank, world)
-    n, E, D, mode = g.num_nodes, g.num_edges, args.dim, args.mode
-    ratios = search.reuse_ratios(L)
-    blk = (n + world - 1) // world
-    n_pad = blk * world
-    r0, r1 = min(rank * blk, n), min((rank + 1) * blk, n)
-    t0 = time.time()
-    i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32))
-    v2 = [i32(L[k]) for k in ("uniqpart_column_index", "uniqpart_pointers", "part2Node_ptr", "part2Node_col")]
-    plan = AggregationPlan.from_v2(n, *v2, rows=(r0, r1), device=dev)
-    plain = AggregationPlan.from_parts(n, i32(g.indices_src), i32(g.indptr_dst), i32(np.arange(n)), rows=(r0, r1),
-                                       device=dev)
-    t_plan = time.time() - t0
-    del v2
-    my_edges = int(g.indptr_dst[r1] - g.indptr_dst[r0])
-    deg = torch.from_numpy(np.maximum(g.degrees_f32(), 1.0)).to(dev)
-
-    from artifact_b200.sharding import PipelinedAggregator, ShardedFeatures
-    gen = torch.Generator(device=dev); gen.manual_seed(1234)
-    feat_x = ShardedFeatures(n, D, rank, world, dev)
-    feat_g = ShardedFeatures(n, D, rank, world, dev)
-    feat_x.full.normal_(generator=gen); feat_g.full.normal_(generator=gen)
-    # this rank's block of features / gradients lives inside the full buffers (in-place all-gather)
-    x_loc = feat_x.local_view()
-    g_loc = feat_g.local_view()
-    out_f = torch.empty((r1 - r0, D), device=dev)
-    out_b = torch.empty((r1 - r0, D), device=dev)
-    ev = lambda: torch.cuda.Event(enable_timing=True)
-    gather_events = []
-    launches = [0]
-    if world == 1 or not args.pipeline:
-        tiles = plan.auto_tiles(D) if args.tiles == "auto" else int(args.tiles)
-    else:
-        tiles = 1                 # the pipeline's stages are already source-blocked
-    pipes = {}
-    if world > 1 and args.pipeline:
-        sched = [[int(k) for k in st.split(",")] for st in args.schedule.split("|")] if args.schedule else None
-        px = PipelinedAggregator(plan, feat_x, schedule=sched)
-        pipes = {id(feat_x): px,
-                 id(feat_g): PipelinedAggregator(plan, feat_g, stage_plans=px.stage_plans, schedule=sched)}
-
-    def one_pass(p, src_loc, feat, out, timed_gather=False):
-        if pipes and p is plan:       # all-gather rounds overlapped with the per-stage aggregation
-            pipe = pipes[id(feat)]
-            pipe.aggregate(None, deg, mode, out)
-            launches[0] += pipe.launches
-            return
-        xs = feat.all_gather(None) if world > 1 else feat.full[:n]
-        p.aggregate(xs, deg, mode, out=out, tiles=tiles, gather_events=gather_events if timed_gather else None)
-        launches[0] += p.last_launch_count()
-
-    def step(p, timed_gather=False):
-        one_pass(p, x_loc, feat_x, out_f, timed_gather)
-        one_pass(p, g_loc, feat_g, out_b, timed_gather)
-
-    def timed(p, steps, warmup, timed_gather=False):
-        for _ in range(warmup):
-            step(p)
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        launches[0] = 0
-        s, e = ev(), ev()
-        w0 = time.time()
-        s.record()
-        for _ in range(steps):
-            step(p, timed_gather)
-        e.record()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        w1 = time.time()
-        ms = torch.tensor([s.elapsed_time(e)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item()) / steps, w0, w1
+    job = Job(args, rank, world, dev, want_plain=(world == 1 and not args.only_kernel))
+    E, D, mode, n = job.E, job.D, job.mode, job.n
 
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
         time.sleep(0.3)
-    ms_step, w0, w1 = timed(plan, args.steps, args.warmup, timed_gather=True)
+    ms_step, w0, w1 = job.timed(job.plan, args.steps, args.warmup, timed_gather=True)
     clocks = sampler.stop(w0, w1) if sampler else None
-    n_launch = launches[0]
+    n_launch = job.launches
     value = 2.0 * E / (ms_step / 1e3)
-
-    # dominant kernel: the phase-B gather of this rank's block, timed by events inside the steps
-    if not gather_events:             # pipelined run: time this rank's whole-block gather kernel on its own
-        xs = feat_x.full[:n]
-        for i in range(8):
-            e0, e1 = ev(), ev()
-            e0.record(); plan.aggregate(xs, deg, mode, out=out_f, phases=2); e1.record()
-            if i >= 3:
-                gather_events.append((e0, e1))
-        torch.cuda.synchronize()
-    # one pass = `tiles` phase-B launches (one per source tile); report the pass as one unit
-    per_pass = max(tiles, 1) if not pipes else 1
-    gms = float(np.sum([a.elapsed_time(b) for a, b in gather_events])) / (len(gather_events) / per_pass)
-    info = plan.info
-    row_b = 4.0 * D
-    gather_bytes = row_b * (info["gather_entries"] + (r1 - r0)) + 4.0 * info["gather_entries"] + 4.0 * (r1 - r0 + 1)
-    if mode == "gcn":
-        gather_bytes += 4.0 * (info["gather_entries"] - info["partial_entries"])
-    achieved = gather_bytes / (gms / 1e3) / 1e9
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
-                "traffic": None, "kernel": "gather_rows_kernel (phase B)", "ms_per_launch": gms,
-                "launches_per_pass": per_pass,
-                "algorithmic_bytes_per_launch": gather_bytes, "peak_kind": f"{peak_kind} copy bandwidth",
-                "note": "algorithmic bytes = (gathered rows + written rows) x 4D + 4 per index; hub rows are "
-                        "re-read from L2, so achieved can exceed the DRAM peak; see profiles/ for DRAM traffic"}
-    if world == 1 and args.scale == 1.0 and args.part_size == WORKLOADS[args.workload][2]:
-        roofline["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(f"{args.workload}:D{D}:{mode}")
+    check = job.check()
+    roofline = job.roofline(hbm_peak, peak_kind)
 
     extra = {}
-    if world == 1 and not args.only_kernel:
-        ms_plain, _, _ = timed(plain, max(3, args.steps // 2), 3)
+    if not args.only_kernel:
+        # L2 -> SM read bandwidth of a plain streaming kernel over a 64 MB buffer: the roof of the gather when
+        # the rows it re-reads are L2-resident (they are: DRAM traffic is a few % of the algorithmic bytes)
+        l2_peak = probe_read_gbs(64 << 20, dev)
+        extra["roofline_l2"] = {"bound": "l2", "achieved": roofline["achieved"], "peak": l2_peak, "unit": "GB/s",
+                                "frac": roofline["achieved"] / l2_peak if l2_peak else None,
+                                "peak_kind": "measured in this run: 128-bit L1-bypassing reads of a 64 MB buffer "
+                                             "(rof_probe_read); the gather also hits L1, so it can read above 1",
+                                "hbm_read_probe_GBs": probe_read_gbs(4 << 30, dev, repeats=2, iters=2)}
+    if job.plain is not None:
+        ms_plain, _, _ = job.timed(job.plain, max(3, args.steps // 2), 3)
         extra["plain"] = {"ms_per_step": ms_plain, "edges_per_s": 2.0 * E / (ms_plain / 1e3),
-                          "algorithmic_GBs": 2 * plain.algorithmic_bytes(D, mode) / ms_plain / 1e6}
+                          "algorithmic_GBs": 2 * job.plain.algorithmic_bytes(D, mode) / ms_plain / 1e6}
         extra["reuse"] = {"ms_per_step": ms_step, "edges_per_s": value,
-                          "algorithmic_GBs": 2 * plan.algorithmic_bytes(D, mode) / ms_step / 1e6}
+                          "algorithmic_GBs": 2 * job.plan.algorithmic_bytes(D, mode) / ms_step / 1e6}
+        extra["reuse_speedup"] = ms_plain / ms_step
+    if world > 1 and not args.only_kernel:
+        extra["breakdown"] = job.breakdown()
+        if job.pipes:
+            extra["stages"] = job.stage_info
 
-    # ---- end to end through the public API with host buffers -----------------------------------
-    def measure_e2e():
-        h_x = torch.empty((blk, D), pin_memory=True); h_x.copy_(x_loc)
-        h_g = torch.empty((blk, D), pin_memory=True); h_g.copy_(g_loc)
-        h_of = torch.empty((r1 - r0, D), pin_memory=True)
-        h_ob = torch.empty((r1 - r0, D), pin_memory=True)
-
-        # the caller's own streams around the API: uploads on one copy stream (the gradient's upload
-        # overlaps the forward pass), downloads on another (the forward result's download overlaps
-        # the backward pass); the aggregation itself runs on the current stream
-        cur = torch.cuda.current_stream(dev)
-        s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
-        up_x, up_g, done_f, done_b, down = (torch.cuda.Event() for _ in range(5))
-        done_f.record(cur); done_b.record(cur)
-
-        def e2e_step():
-            with torch.cuda.stream(s_in):
-                s_in.wait_event(done_f)                    # previous forward pass has read x
-                x_loc.copy_(h_x, non_blocking=True); up_x.record(s_in)
-                s_in.wait_event(done_b)
-                g_loc.copy_(h_g, non_blocking=True); up_g.record(s_in)
-            cur.wait_event(up_x)
-            one_pass(plan, x_loc, feat_x, out_f); done_f.record(cur)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(done_f)
-                h_of.copy_(out_f, non_blocking=True)
-            cur.wait_event(up_g)
-            one_pass(plan, g_loc, feat_g, out_b); done_b.record(cur)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(done_b)
-                h_ob.copy_(out_b, non_blocking=True); down.record(s_out)
-            cur.wait_event(down)                           # the step ends when both results are on the host
-
-        e2e_steps = max(3, min(args.steps, 10))
-        for _ in range(3):
-            e2e_step()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        s, e = ev(), ev()
-        s.record()
-        for _ in range(e2e_steps):
-            e2e_step()
-        e.record()
-        torch.cuda.synchronize()
-        ms_e2e = torch.tensor([s.elapsed_time(e) / e2e_steps], device=dev)
-        if world > 1:
-            dist.all_reduce(ms_e2e, op=dist.ReduceOp.MAX)
-        ms_e2e = float(ms_e2e.item())
-        e2e = {"value": 2.0 * E / (ms_e2e / 1e3), "unit": "edges/s", "ms_per_step": ms_e2e,
-               "h2d_bytes_per_step": 2 * blk * D * 4 * world, "d2h_bytes_per_step": 2 * n * D * 4,
-               "note": "features and gradients copied from pinned host memory, both results copied back, every step; "
-                       "the graph plan stays resident like upstream's inputInfo tensors"}
-        return e2e
-
-    e2e = None if args.only_kernel else measure_e2e()
+    e2e = None if args.only_kernel else job.e2e(max(3, min(args.steps, 10)))
 
     # ---- width / mode sweep (single GPU only; informational) -----------------------------------
     if world == 1 and not args.no_sweep:
+        from artifact_b200.plan import empty_padded
         sweep = []
-        for d in (32, 64, 128, 256, 602):
-            xs = torch.randn((n, d), device=dev)
+        for d in (7, 32, 47, 64, 100, 128, 256, 602):
+            xs = empty_padded(n, d, dev); xs.normal_()
             o = torch.empty((n, d), device=dev)
-            for m in ("sum", "mean"):
+            for m in ("sum", "mean", "gcn"):
                 row = {"D": d, "mode": m}
-                for nm, p in (("reuse", plan), ("plain", plain)):
+                for nm, p in (("reuse", job.plan), ("plain", job.plain)):
                     t = p.auto_tiles(d)
                     row[nm + "_tiles"] = t
                     for _ in range(3):
-                        p.aggregate(xs, deg, m, out=o, tiles=t)
-                    s, e = ev(), ev()
+                        p.aggregate(xs, job.deg, m, out=o, tiles=t)
+                    s, e = job.ev(), job.ev()
                     s.record()
                     for _ in range(5):
-                        p.aggregate(xs, deg, m, out=o, tiles=t)
+                        p.aggregate(xs, job.deg, m, out=o, tiles=t)
                     e.record(); torch.cuda.synchronize()
                     ms = s.elapsed_time(e) / 5
                     row[nm] = {"ms": round(ms, 4), "gedges_per_s": round(E / ms / 1e6, 3),
@@ -499,26 +747,29 @@ def main():
                 sweep.append(row)
             del xs, o
         extra["sweep_forward_pass"] = sweep
+        extra["sweep_note"] = "feature rows padded to a multiple of 4 floats (what the drop-in entry points allocate)"
 
     # ---- one GCN layer through the drop-in layer API (informational: "GCN layer ms") -----------
     if world == 1 and not args.no_sweep:
         from artifact_b200.models import ROF_inputInfo
         from artifact_b200.reuse_conv import ROF_GCNConv
-        f_in = {"c2": 602, "c4": 100, "c5": 64}[args.workload]
-        t = lambda k: i32(L[k]).to(dev)
-        info = ROF_inputInfo(None, None, deg, None, None, args.part_size, 4, None, None, None,
+        i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32))
+        f_in = {"c2": 602, "c3": 128, "c4": 100, "c5": 64}[args.workload]
+        t = lambda k: i32(job.L[k]).to(dev)
+        info = ROF_inputInfo(None, None, job.deg, None, None, args.part_size, 4, None, None, None,
                              t("uniqpart_column_index"), t("uniqpart_pointers"), t("part2Node_ptr"), t("part2Node_col"))
         layer = ROF_GCNConv(f_in, D, add_self_loops=False, kernel_type="ROF_v2").to(dev)
         xin = torch.randn((n, f_in), device=dev, requires_grad=True)
+        gout = job.feat_g.full[:n]
 
         def layer_step():
             y = layer(xin, info)
-            y.backward(feat_g.full[:n])
+            y.backward(gout)
             xin.grad = None; layer.zero_grad(set_to_none=True)
 
         for _ in range(3):
             layer_step()
-        s, e = ev(), ev()
+        s, e = job.ev(), job.ev()
         s.record()
         for _ in range(5):
             layer_step()
@@ -528,32 +779,66 @@ def main():
             w_ = layer.weight.detach()
             s.record()
             for _ in range(5):
-                tmp = torch.mm(xin, w_); torch.mm(feat_g.full[:n], w_.t()); torch.mm(xin.t(), feat_g.full[:n])
+                torch.mm(xin, w_); torch.mm(gout, w_.t()); torch.mm(xin.t(), gout)
             e.record(); torch.cuda.synchronize()
         ms_mm = s.elapsed_time(e) / 5
         extra["gcn_layer"] = {"shape": [n, f_in, D], "kernel_type": "ROF_v2", "fwd_bwd_ms": round(ms_layer, 3),
                               "of_which_dense_mm_ms": round(ms_mm, 3),
                               "note": "ROF_GCNConv forward+backward; the three fp32 GEMMs (X.W, dX, dW) stay on cuBLAS"}
         del info, layer, xin
+        from artifact_b200 import ops
+        ops.clear_plan_cache()
+
+    if world == 1 and not args.no_upstream and args.workload == "c2" and args.scale == 1.0:
+        try:
+            extra["upstream_gpu"] = upstream_gpu(job)
+        except Exception as ex:                          # never lose the headline to the comparison
+            extra["upstream_gpu"] = {"skipped": f"{type(ex).__name__}: {ex}"[:300]}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cb = cpu_plain(job.g, D, mode, seconds_budget=20.0, steps=3, warmup=1)
+        cpu = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        try:
+            extra["cpu_torch_sparse"] = cpu_torch_sparse(job.g, D)
+        except Exception as ex:
+            extra["cpu_torch_sparse"] = {"skipped": f"{type(ex).__name__}: {ex}"[:300]}
+
+    line = {
+        "metric": "aggregation edges/s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args, job.g, job.ratios),
+        "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": n_launch, "clocks": clocks,
+        "check": check,
+        "setup_s": {"graph": round(job.t_graph, 2), "reuse_search": round(job.t_search, 2), "plans": round(job.t_plan, 2)},
+        "shard": {"rows": job.r1 - job.r0, "edges_rank0": int(job.g.indptr_dst[job.r1] - job.g.indptr_dst[job.r0])},
+    }
+    line.update(extra)
+    ok = check["ok"]
+    job.release()
+
+    # ---- the other benchmark configurations, same machinery, so that the record carries them ----
+    if not args.no_configs:
+        configs = {}
+        names = [w for w in ("c4", "c5") if w != args.workload] + (["c3"] if world == 1 and args.workload != "c3" else [])
+        for name in names:
+            try:
+                configs[name] = side_config(name, args, rank, world, dev, steps=max(3, min(args.steps, 10)))
+                ok = ok and configs[name]["check"]["ok"]
+            except Exception as ex:
+                if world > 1:
+                    raise                                # ranks must not diverge around collectives
+                configs[name] = {"skipped": f"{type(ex).__name__}: {ex}"[:300]}
+        line["configs"] = configs
 
     if rank == 0:
-        cpu = None
-        if world == 1 and not args.no_cpu:
-            cb = cpu_plain(g, D, mode, seconds_budget=20.0, steps=3, warmup=1)
-            cpu = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        line = {
-            "metric": "aggregation edges/s", "value": value, "unit": "edges/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": workload_config(args, g, ratios),
-            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": n_launch, "clocks": clocks,
-            "setup_s": {"graph": round(t_graph, 2), "reuse_search": round(t_search, 2), "plans": round(t_plan, 2)},
-            "shard": {"rows": r1 - r0, "edges_rank0": my_edges},
-        }
-        line.update(extra)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if not ok:
+        sys.stderr.write("bench.py: the output check failed (see \"check\" in the JSON line)\n")
+        sys.exit(3)
 
 
 if __name__ == "__main__":

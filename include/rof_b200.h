@@ -235,7 +235,13 @@ int rof_aggregate_fused(const rof_plan* plan, int phases, int mode, const float*
  *   - A pass whose rof_plan_workspace_bytes(plan, dim) exceeds ROF_STATIC_SCRATCH_BYTES returns
  *     ROF_ERR_WORKSPACE and launches nothing.
  *   - The first call on each device looks up the array's device address; make that call during
- *     start-up, with the device current, before any stream capture begins.
+ *     start-up, with the device current, before any stream capture begins.  With CUDA's lazy
+ *     module loading that first call is also where the array gets its 32 MiB of device memory: a
+ *     host that hands the rest of HBM to its own pool must make the call before it does so (a full
+ *     valid pass — the address is looked up after the arguments have been checked).
+ *   - The address is cached per device ordinal for the life of the process.  After
+ *     cudaDeviceReset() (or any other teardown of the device's primary context) the cached address
+ *     is stale and the entry point must not be used again in that process.
  *   - All calls on a GPU share the array, which keeps the previous call's contents (each pass
  *     writes every scratch row before reading it, so nothing has to be cleared).  Calls that
  *     overlap on the GPU race on it: keep them ordered on one stream.

@@ -214,3 +214,28 @@ def test_sum_aggregate_gradient_matches_dense_autograd(mode):
     (yd * w.double()).sum().backward()
     assert_close(y.detach().cpu().numpy(), yd.detach().cpu().numpy(), what=f"{mode} forward")
     assert_close(h.grad.cpu().numpy(), hd.grad.cpu().numpy(), what=f"{mode} gradient")
+
+
+@pytest.mark.parametrize("kernel_type", ["GNNA", "ROF_v1", "ROF_v2"])
+def test_aggregate_first_order_gives_the_same_layer(kernel_type):
+    """transform_order='auto' with a narrow input: A_hat (x W) computed as (A_hat x) W; outputs and all
+    three gradients must agree with the reference order (symmetric graph: the backward is exact)"""
+    g, info = make_info("c1_full_ps2")
+    n = g["N"]
+    torch.manual_seed(11)
+    ref = ROF_GCNConv(6, 20, add_self_loops=False, kernel_type=kernel_type, reuse_size=info.reuse_size).to(DEV)
+    alt = ROF_GCNConv(6, 20, add_self_loops=False, kernel_type=kernel_type, reuse_size=info.reuse_size,
+                      transform_order="auto").to(DEV)
+    alt.load_state_dict(ref.state_dict())
+    x1 = torch.randn((n, 6), device=DEV, requires_grad=True)
+    x2 = x1.detach().clone().requires_grad_()
+    w = torch.randn((n, 20), device=DEV)
+    y1 = ref(x1, info); (y1 * w).sum().backward()
+    y2 = alt(x2, info); (y2 * w).sum().backward()
+    assert_close(y2.detach().cpu().numpy(), y1.detach().cpu().numpy(), rel=2e-5, what="forward")
+    assert_close(x2.grad.cpu().numpy(), x1.grad.cpu().numpy(), rel=5e-5, abs_=1e-5, what="dX")
+    assert_close(alt.weight.grad.cpu().numpy(), ref.weight.grad.cpu().numpy(), rel=5e-5, abs_=2e-4, what="dW")
+    # a wide input keeps the reference order
+    wide = ROF_GCNConv(20, 6, add_self_loops=False, kernel_type=kernel_type, reuse_size=info.reuse_size,
+                       transform_order="auto").to(DEV)
+    assert wide(torch.randn((n, 20), device=DEV), info).shape == (n, 6)

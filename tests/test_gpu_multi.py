@@ -50,7 +50,19 @@ def _worker(rank, world, port, name, q):
         for _ in range(2):
             pipe2.aggregate(local, deg, mode, out2)
         torch.cuda.synchronize()
-        res[mode] = (a, out.cpu().numpy(), out2.cpu().numpy())
+        # blocks of equal work instead of equal row counts, transfer stages cut into small compute stages
+        from artifact_b200.sharding import row_blocks
+        _, bal = row_blocks(n, world, indptr=g["indptr_dst"])
+        b0, b1 = bal[rank]
+        feats_b = ShardedFeatures(n, dim, rank, world, dev, bounds=bal)
+        feats_b.local_view().copy_(torch.from_numpy(x[b0:b1]).to(dev))
+        plan_b = AggregationPlan.from_v2(n, *[i32(a_) for a_ in layout_args(g["layouts"], "v2")], rows=(b0, b1))
+        out3 = torch.empty((b1 - b0, dim), device=dev)
+        pipe3 = PipelinedAggregator(plan_b, feats_b, tile_bytes=n * dim * 4 / 6)
+        for _ in range(2):
+            pipe3.aggregate(None, deg, mode, out3)
+        torch.cuda.synchronize()
+        res[mode] = (a, out.cpu().numpy(), out2.cpu().numpy(), (b0, out3.cpu().numpy()))
     gathered = [None] * world
     dist.all_gather_object(gathered, (r0, res))
     if rank == 0:
@@ -90,3 +102,27 @@ def test_sharded_and_pipelined_match_oracle(name):
         assert_close(piped, want, what=f"pipelined, {mode}")
         piped2 = np.concatenate([r[mode][2] for _, r in sorted(gathered, key=lambda t: t[0])])
         assert_close(piped2, want, what=f"pipelined, two half stages, {mode}")
+        piped3 = np.concatenate([o for _, o in sorted((r[mode][3] for _, r in gathered), key=lambda t: t[0])])
+        assert_close(piped3, want, what=f"pipelined, blocks of equal work, tiled stages, {mode}")
+
+
+def test_static_scratch_entry_point_on_a_second_device():
+    """the built-in scratch array exists once per GPU and its address is looked up per device: the
+    no-allocation entry point must work on cuda:1 of the same process, before and after cuda:0"""
+    import rof_oracle
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least 2 GPUs")
+    from artifact_b200.plan import AggregationPlan
+    from conftest import assert_close
+    g = load_golden("c5_n1024_ps2")
+    n, L = g["N"], g["layouts"]
+    x = np.random.default_rng(9).standard_normal((n, 40)).astype(np.float32)
+    want = rof_oracle.aggregate_v2(x, L["uniqpart_column_index"], g["degrees"], L["uniqpart_pointers"],
+                                   L["part2Node_ptr"], L["part2Node_col"], "sum", exact64=True)
+    for d in (1, 0, 1):
+        dev = torch.device("cuda", d)
+        i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+        plan = AggregationPlan.from_v2(n, *[i32(a) for a in layout_args(L, "v2")], device=dev)
+        got = plan.aggregate_static_scratch(torch.from_numpy(x).to(dev), None, "sum")
+        assert got.device == dev
+        assert_close(got.cpu().numpy(), want, what=f"static scratch on cuda:{d}")

@@ -58,6 +58,38 @@ def test_static_scratch_matches_workspace_entry_point_call_after_call():
         assert torch.equal(got, want)                                     # same kernels, same order: bit-identical
 
 
+def test_static_scratch_against_the_cpu_oracle():
+    """the same entry point judged by the CPU oracle instead of by the library's other entry point"""
+    import rof_oracle
+    g, rp = reuse_plan()
+    L = g["layouts"]
+    rng = np.random.default_rng(12)
+    deg_np = np.maximum(g["degrees"], 1.0)
+    deg = torch.from_numpy(deg_np).to(DEV)
+    for dim, mode in ((36, "gcn"), (64, "sum")):
+        x = rng.standard_normal((g["N"], dim)).astype(np.float32)
+        want = rof_oracle.aggregate_v2(x, L["uniqpart_column_index"], deg_np, L["uniqpart_pointers"],
+                                       L["part2Node_ptr"], L["part2Node_col"], mode, True)
+        for call in range(2):
+            got = rp.aggregate_static_scratch(torch.from_numpy(x).to(DEV), deg, mode)
+            assert_close(got.cpu().numpy(), want, what=f"static scratch vs oracle, {mode} dim {dim}, call {call}")
+
+
+def test_static_scratch_checks_its_tensors_like_aggregate():
+    g, rp = reuse_plan()
+    n = g["N"]
+    x = torch.zeros((n, 16), device=DEV)
+    deg = torch.ones(n, device=DEV)
+    with pytest.raises(RuntimeError):
+        rp.aggregate_static_scratch(x, deg, "sum", out=torch.zeros((16, n), device=DEV).t())   # column stride != 1
+    with pytest.raises(RuntimeError):
+        rp.aggregate_static_scratch(x, torch.ones(2 * n, device=DEV)[::2], "gcn")               # strided degrees
+    with pytest.raises(RuntimeError):
+        rp.aggregate_static_scratch(x, torch.ones(n), "gcn")                                    # degrees on the host
+    with pytest.raises(RuntimeError):
+        rp.aggregate_static_scratch(x, deg, "sum", out=torch.zeros((n, 16)))                    # out on the host
+
+
 def test_static_scratch_refuses_what_does_not_fit():
     g, rp = reuse_plan()
     dim = 40000                                            # 261 partial rows x 160 KB > 32 MiB
