@@ -27,8 +27,9 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-Xcompiler", "-fPIC,-fopenmp,-O3",
     "--expt-relaxed-constexpr",
-    # each gathered term is an un-fused multiply followed by an add, like upstream's
-    # __fmul_rn + add (reuse_conv_kernel.cu:270); never contract them into an FMA
+    # no implicit contraction: the kernels round where the source says so.  The GCN terms use an
+    # explicit fused multiply-add (one rounding where upstream's __fmul_rn + add has two,
+    # reuse_conv_kernel.cu:270); scales, epilogue and the pre-scaling pass are separate roundings
     "-fmad=false",
 ]
 

@@ -150,6 +150,7 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
     a.x = x; a.ldx = ldx; a.partials = nullptr; a.ldp = 0; a.degrees = degrees;
     a.out = partials; a.ldo = w.ld; a.slots = nullptr; a.lds = 0;
     a.mirror = cache_result; a.ldm = (int64_t)dim + 1; a.mirror_flag_col = cache_result ? dim : -1;
+    a.mirror_ids = p->d_group_orig;
     a.num_nodes = p->num_nodes; a.row_begin = 0; a.dim = dim; a.weight_gcn = gcn; a.scale_mode = 0;
     a.out_padded = 1; a.kernel = kernel_for(p->num_groups, p->group_sources); a.status = p->d_status;
     e = launch_gather(a, stream, &g_last_launches);

@@ -167,7 +167,8 @@ __device__ __forceinline__ void finish_final(const GatherArgs& a, int row, int c
       if (t < valid) op[t] = r[t];
   }
   if (a.mirror != nullptr) {
-    float* mp = a.mirror + (int64_t)row * a.ldm + col0;
+    const int mrow = a.mirror_ids != nullptr ? __ldg(a.mirror_ids + row) : row;
+    float* mp = a.mirror + (int64_t)mrow * a.ldm + col0;
 #pragma unroll
     for (int t = 0; t < VEC; ++t)
       if (t < valid) mp[t] = r[t];
@@ -385,7 +386,7 @@ __global__ void __launch_bounds__(256, (C <= 2 ? 4 : (C * U <= 6 ? 3 : (C * U <=
     for (int k = 0; k < C; ++k)
       if (active[k]) finish_final<VEC>(a, dst, (lane + k * L) * VEC, acc[k], scale);
     if (a.mirror != nullptr && a.mirror_flag_col >= 0 && lane == 0)
-      a.mirror[(int64_t)dst * a.ldm + a.mirror_flag_col] = 1.0f;
+      a.mirror[(int64_t)(a.mirror_ids != nullptr ? __ldg(a.mirror_ids + dst) : dst) * a.ldm + a.mirror_flag_col] = 1.0f;
   } else {
     finish_segment<VEC, C>(a, -dst - 1, acc, active, true, lane, L, lane == 0, gmask, group_lane0);
   }
@@ -565,7 +566,7 @@ __global__ void __launch_bounds__(256) gather_rows_ring_kernel(const __grid_cons
       for (int k = 0; k < C; ++k)
         if (active[k]) finish_final<4>(a, dst, (vi + k * LPR) * 4, acc[k], scale);
       if (a.mirror != nullptr && a.mirror_flag_col >= 0 && lane == 0)
-        a.mirror[(int64_t)dst * a.ldm + a.mirror_flag_col] = 1.0f;
+        a.mirror[(int64_t)(a.mirror_ids != nullptr ? __ldg(a.mirror_ids + dst) : dst) * a.ldm + a.mirror_flag_col] = 1.0f;
     }
   } else {
     finish_segment<4, C>(a, -dst - 1, acc, active, sr == 0, vi, LPR, lane == 0, 0xffffffffu, 0);

@@ -125,6 +125,18 @@ int64_t shared_ids_of_tile(const std::vector<int32_t>& ents, std::vector<int32_t
   return saved;
 }
 
+}  // namespace
+
+// Smallest share of the gathered rows that reuse groups must save for a ROF_v2 plan to use them
+// (ROF_REUSE_MIN overrides, e.g. 0 to always use the groups the search found).
+double reuse_min_saving() {
+  const char* e = std::getenv("ROF_REUSE_MIN");
+  if (e != nullptr && e[0] != '\0') return std::atof(e);
+  return kMinReuseSaving;
+}
+
+namespace {
+
 // ROF_TILES=0 never builds tiles, ROF_TILES=1 always does (when there are eligible rows); unset:
 // tiles are built when a sample of them saves at least kTileMinSaved of the global row reads.
 int tiles_override() {
@@ -359,6 +371,7 @@ static int finalize_plan_impl(HostPlan& hp, rof_plan** out, cudaStream_t stream)
 
   p->h_row_ptr = hp.row_ptr;
   p->h_group_ptr = hp.group_ptr;
+  if ((int)hp.group_orig.size() == p->num_groups) p->h_group_orig = hp.group_orig;
   p->h_items = items;
   p->h_split = split;
   if (p->device < 0) {
@@ -397,6 +410,8 @@ static int finalize_plan_impl(HostPlan& hp, rof_plan** out, cudaStream_t stream)
   if (rc == ROF_OK) rc = upload((void**)&p->d_items, items.data(), sizeof(WorkItem) * items.size(), "upload work items");
   if (rc == ROF_OK) rc = upload((void**)&p->d_group_items, gitems.data(), sizeof(WorkItem) * gitems.size(), "upload group items");
   if (rc == ROF_OK) rc = upload((void**)&p->d_split, split.data(), sizeof(SplitRow) * split.size(), "upload split rows");
+  if (rc == ROF_OK && (int)hp.group_orig.size() == p->num_groups)
+    rc = upload((void**)&p->d_group_orig, hp.group_orig.data(), sizeof(int32_t) * hp.group_orig.size(), "upload group ids");
   if (rc == ROF_OK) rc = upload((void**)&p->fine.d_items, fine_items.data(), sizeof(WorkItem) * fine_items.size(), "upload work items (narrow rows)");
   if (rc == ROF_OK) rc = upload((void**)&p->fine.d_split, fine_split.data(), sizeof(SplitRow) * fine_split.size(), "upload split rows (narrow rows)");
   // which split row every scratch slot belongs to, and the rows' arrival counters (zero between passes)
@@ -591,18 +606,39 @@ int rof_plan_create_v2(rof_plan** plan, int where, int num_nodes, int row_begin,
   hp.num_nodes = num_nodes; hp.row_begin = row_begin; hp.row_end = row_end;
   const int rows = row_end - row_begin;
   try {
-    // A unique part becomes a reuse group when at least two destinations of this plan's
-    // row block share it and it has at least two sources; otherwise its sources are
-    // listed inline in the destination's row (a one-source "partial" is the source itself).
+    // A unique part becomes a reuse group — its partial sum is built once in phase A and read as
+    // one row by each of its destinations — when that saves row traffic inside this plan's row
+    // block: `local` destinations read 1 row instead of `len`, at the price of `len` reads and one
+    // write in phase A.  Otherwise its sources are listed inline in the destination's row.
+    // And reuse is used at all only when it saves a worthwhile share of the gathered rows
+    // (reuse_min_saving(): below that the partial rows cost more L2 than the reads they replace;
+    // measured on the 114.6M- and 123.8M-edge power-law graphs, 6.5 % and 2.8 % saved: 1-2 % slower).
+    // With ROF_REUSE_MIN <= 0 every part shared by two local destinations is a group, as the search
+    // picked them.
+    const double min_saving = reuse_min_saving();
+    auto worth = [min_saving](int local, int32_t len) {
+      if (local < 2 || len < 2) return false;
+      return min_saving <= 0.0 || (int64_t)local * (len - 1) > len + 1;
+    };
     std::vector<int32_t> group_of((size_t)num_uniqparts, -1);
-    hp.group_ptr.assign(1, 0);
-    hp.row_ptr.assign((size_t)rows + 1, 0);
+    std::vector<int32_t> local_of((size_t)num_uniqparts, 0);
+    int64_t saved = 0, total = 0;
     for (int u = 0; u < num_uniqparts; ++u) {
       const int32_t len = up.ptr[u + 1] - up.ptr[u];
       int local = 0;
       for (int32_t k = np_.ptr[u]; k < np_.ptr[u + 1]; ++k) local += (nc.ptr[k] >= row_begin && nc.ptr[k] < row_end);
+      local_of[(size_t)u] = local;
+      total += (int64_t)local * len;
+      if (worth(local, len)) saved += (int64_t)local * (len - 1) - (len + 1);
+    }
+    const bool use_groups = total > 0 && (min_saving <= 0.0 || (double)saved >= min_saving * (double)total);
+    hp.group_ptr.assign(1, 0);
+    hp.row_ptr.assign((size_t)rows + 1, 0);
+    for (int u = 0; u < num_uniqparts; ++u) {
+      const int32_t len = up.ptr[u + 1] - up.ptr[u];
+      const int local = local_of[(size_t)u];
       if (local == 0 || len == 0) continue;
-      const bool grouped = local >= 2 && len >= 2;
+      const bool grouped = use_groups && worth(local, len);
       if (grouped) {
         group_of[u] = (int32_t)hp.group_ptr.size() - 1;
         hp.group_col.insert(hp.group_col.end(), col.ptr + up.ptr[u], col.ptr + up.ptr[u + 1]);
@@ -673,6 +709,7 @@ void rof_plan_destroy(rof_plan* p) {
   cudaFree(p->d_col);
   cudaFree(p->d_items);
   cudaFree(p->d_group_items);
+  cudaFree(p->d_group_orig);
   cudaFree(p->d_split);
   cudaFree(p->fine.d_items);
   cudaFree(p->fine.d_split);

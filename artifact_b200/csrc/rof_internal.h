@@ -36,6 +36,7 @@ constexpr int kNarrowRowFloats = 32;          // rows up to this width use the f
 // row order); the entries that occur at least twice inside a tile — partial rows of reuse groups
 // and feature rows that several of the tile's destinations gather — are staged once in shared
 // memory (at most kTileMaxStage rows) and read from there.
+constexpr double kMinReuseSaving = 0.15;      // ROF_v2 plans: reuse groups are used when they save at least this share of the gathered rows
 constexpr int kTileRows = 32;
 constexpr int kTileMaxRowEntries = 256;
 constexpr int kTileMaxStage = 64;
@@ -73,6 +74,9 @@ struct rof_plan {
   int32_t* d_col = nullptr;           // [gather_entries + group_sources]: phase-B entries, then group sources
   rof::WorkItem* d_items = nullptr;   // [num_items] phase B, longest first
   rof::WorkItem* d_group_items = nullptr;  // [num_groups] phase A (begin/end index d_col)
+  // stage / tile plans: the id each group has in the plan they were split from (the row of the
+  // caller's part_result_cache it fills); null for a plan built from index tensors (identity)
+  int32_t* d_group_orig = nullptr;
   rof::SplitRow* d_split = nullptr;   // [num_split_rows]
   int32_t* d_slot_owner = nullptr;    // [num_slots]: index into d_split of the row a slot belongs to
   int32_t* d_arrive = nullptr;        // [num_split_rows]: segments of the row seen so far in this pass (0 between passes)
@@ -116,6 +120,7 @@ struct rof_plan {
   // only when there is no device to read them back from
   std::vector<int64_t> h_row_ptr;
   std::vector<int32_t> h_group_ptr;
+  std::vector<int32_t> h_group_orig;   // host copy of d_group_orig (empty: identity)
   std::vector<rof::WorkItem> h_items;
   std::vector<rof::SplitRow> h_split;
   std::vector<int32_t> h_col;
@@ -136,10 +141,12 @@ struct HostPlan {
   std::vector<int32_t> col;           // < num_nodes: feature row; >= num_nodes: partial row (col - num_nodes)
   std::vector<int32_t> group_ptr;     // [G+1] into group_col
   std::vector<int32_t> group_col;     // sources of each group
+  std::vector<int32_t> group_orig;    // optional: id of each group in the plan this one was split from
   int64_t original_edges = 0;
 };
 
 int finalize_plan(HostPlan& hp, rof_plan** out, cudaStream_t stream);
+double reuse_min_saving();
 
 // Optional fused epilogue of a final output row: out = act(result + self_scale * self_x[row] + bias)
 struct Epilogue {
@@ -161,6 +168,7 @@ struct GatherArgs {
   float* slots;          int64_t lds;        // dst < 0
   float* mirror;         int64_t ldm;        // optional second copy of the dst>=0 rows
   int mirror_flag_col;                       // column of `mirror` that receives 1.0f per row, or -1
+  const int32_t* mirror_ids;                 // optional: row of `mirror` for each dst (null: dst itself)
   int num_nodes;
   int row_begin;
   int dim;

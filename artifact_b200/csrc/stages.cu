@@ -35,6 +35,7 @@ int split_by_row_stage(const rof_plan* whole, const std::vector<int32_t>& row_st
       for (int32_t k = gptr[g]; k < gptr[g + 1]; ++k) st = std::max(st, (int)stage_of(gcol[(size_t)k]));
       gstage[g] = st;
       glocal[g] = (int32_t)hp[st].group_ptr.size() - 1;
+      hp[st].group_orig.push_back(whole->h_group_orig.empty() ? g : whole->h_group_orig[(size_t)g]);
       hp[st].group_col.insert(hp[st].group_col.end(), gcol.begin() + gptr[g], gcol.begin() + gptr[g + 1]);
       hp[st].group_ptr.push_back((int32_t)hp[st].group_col.size());
     }

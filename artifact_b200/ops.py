@@ -10,11 +10,12 @@ What differs from upstream, on purpose:
 * a graph without any reuse group (G = 0) works (upstream: "invalid configuration argument"
   then exit(-1), reuse_conv_kernel.cu:650-652, 709-714);
 * errors raise RuntimeError; the process is never killed;
-* the GCN entry points hoist upstream's per-neighbour factor rsqrt(degrees[n]) (recomputed by every
-  lane for every neighbour, reuse_conv_kernel.cu:254, 914) into one pass over `tmp = X.W`
-  (`rof_scale_rows`) and aggregate in ROF_MODE_GCN_PRESCALED: the same products, one rsqrt per node;
-* `tmp` is allocated with a row stride padded to a multiple of 4 floats, so widths such as 7, 47
-  or 602 still run on 128-bit loads.
+* `tmp = X.W` is allocated with a row stride padded to a multiple of 4 floats, so widths such as 7,
+  47 or 602 still run on 128-bit loads; a `d_output` whose rows are not 16-byte aligned is copied
+  into such a buffer, and that copy applies upstream's per-neighbour factor rsqrt(degrees[n])
+  (reuse_conv_kernel.cu:254, 914) on the way (`rof_scale_rows` + ROF_MODE_GCN_PRESCALED).  Aligned
+  inputs keep the factor inside the gather kernel: hoisting it into a pass of its own measured
+  slower on B200 (the kernel is bound by memory, not by the multiply).
 
 Each distinct set of index tensors is turned into an AggregationPlan the first time it is
 seen and cached; the cache holds the tensors, so their addresses cannot be reused while the
@@ -89,19 +90,24 @@ def _cache_arg(plan, part_result_cache, dim):
     return c
 
 
-def _transform_scaled(input, weight, degrees):
-    """tmp = rsqrt(degrees) * (input @ weight), rows padded to a multiple of 4 floats
-    (upstream: tmp = torch::mm(input, weight), reuse_conv_kernel.cu:302, 621, 971; the factor is
-    applied per neighbour inside its kernels)."""
+def _transform(input, weight):
+    """tmp = input @ weight with rows padded to a multiple of 4 floats (upstream: tmp =
+    torch::mm(input, weight), reuse_conv_kernel.cu:302, 621, 971)"""
     d = weight.size(1)
     ld = padded_width(d)
-    if ld != d:
-        w = torch.zeros((weight.size(0), ld), dtype=weight.dtype, device=weight.device)
-        w[:, :d] = weight
-        tmp = torch.mm(input, w)[:, :d]
-    else:
-        tmp = torch.mm(input, weight)
-    return scale_rows(tmp, degrees, "rsqrt", out=tmp)
+    if ld == d:
+        return torch.mm(input, weight)
+    w = torch.zeros((weight.size(0), ld), dtype=weight.dtype, device=weight.device)
+    w[:, :d] = weight
+    return torch.mm(input, w)[:, :d]
+
+
+def _gcn_rows(x, degrees):
+    """-> (rows the gather kernels can read with 128-bit loads, mode): x itself in GCN mode when its
+    rows are 16-byte aligned, else a padded copy already multiplied by rsqrt(degrees)"""
+    if x.size(1) % 4 == 0 and x.data_ptr() % 16 == 0 and x.stride(0) % 4 == 0:
+        return x, "gcn"
+    return scale_rows(x, degrees, "rsqrt"), "gcn_prescaled"
 
 
 def _aligned_rows(x):
@@ -125,7 +131,8 @@ def aggregate_gcn(kernel_type, info, x):
                            info.part2Node_col)
     else:
         raise NotImplementedError
-    return plan.aggregate(_aligned_rows(x.contiguous()), info.degrees, "gcn", tiles="auto")
+    xs, mode = _gcn_rows(x.contiguous(), info.degrees)
+    return plan.aggregate(xs, info.degrees, mode, tiles="auto")
 
 
 def _backward_tail(d_input_prime, X, weight):
@@ -150,8 +157,8 @@ def GNNA_forward(input, weight, column_index, degrees, part_pointers, part2Node,
                  (part_pointers, "part_pointers"), (part2Node, "part2Node")):
         _check_input(t, n)
     plan = plan_for_parts(input.size(0), column_index, part_pointers, part2Node)
-    tmp = _transform_scaled(input, weight, degrees)                 # reuse_conv_kernel.cu:302
-    return [plan.aggregate(tmp, degrees, "gcn_prescaled", tiles="auto")]
+    tmp = _transform(input, weight)                                 # reuse_conv_kernel.cu:302
+    return [plan.aggregate(tmp, degrees, "gcn", tiles="auto")]
 
 
 def GNNA_backward(d_output, X, weight, column_index, degrees, part_pointers, part2Node, partSize, dimWorker,
@@ -160,8 +167,8 @@ def GNNA_backward(d_output, X, weight, column_index, degrees, part_pointers, par
                  (degrees, "degrees"), (part_pointers, "part_pointers"), (part2Node, "part2Node")):
         _check_input(t, n)
     plan = plan_for_parts(d_output.size(0), column_index, part_pointers, part2Node)
-    ds = scale_rows(d_output, degrees, "rsqrt")
-    return _backward_tail(plan.aggregate(ds, degrees, "gcn_prescaled", tiles="auto"), X, weight)
+    ds, mode = _gcn_rows(d_output, degrees)
+    return _backward_tail(plan.aggregate(ds, degrees, mode, tiles="auto"), X, weight)
 
 
 # ---- reuse_conv.cpp:208-285 ---------------------------------------------------------------
@@ -174,8 +181,8 @@ def reuse_forward_v1(input, weight, column_index, degrees, part_pointers, part2N
         _check_input(t, n)
     plan = plan_for_v1(input.size(0), column_index, part_pointers, part2Node, part_cache_flagindex,
                        part_pointers_cache, column_index_cache)
-    tmp = _transform_scaled(input, weight, degrees)                 # reuse_conv_kernel.cu:621
-    return [plan.aggregate(tmp, degrees, "gcn_prescaled",
+    tmp = _transform(input, weight)                                 # reuse_conv_kernel.cu:621
+    return [plan.aggregate(tmp, degrees, "gcn", tiles="auto",
                            cache_result=_cache_arg(plan, part_result_cache, tmp.size(1)))]
 
 
@@ -188,8 +195,8 @@ def reuse_backward_v1(d_output, X, W, column_index, degrees, part_pointers, part
         _check_input(t, n)
     plan = plan_for_v1(d_output.size(0), column_index, part_pointers, part2Node, part_cache_flagindex,
                        part_pointers_cache, column_index_cache)
-    ds = scale_rows(d_output, degrees, "rsqrt")
-    dp = plan.aggregate(ds, degrees, "gcn_prescaled",
+    ds, mode = _gcn_rows(d_output, degrees)
+    dp = plan.aggregate(ds, degrees, mode, tiles="auto",
                         cache_result=_cache_arg(plan, part_result_cache, d_output.size(1)))
     return _backward_tail(dp, X, W)
 
@@ -202,8 +209,8 @@ def reuse_forward_v2(input, weight, uniqpart_column_index, degrees, uniqpart_poi
                  (part2Node_col, "part2Node_col")):
         _check_input(t, n)
     plan = plan_for_v2(input.size(0), uniqpart_column_index, uniqpart_pointers, part2Node_ptr, part2Node_col)
-    tmp = _transform_scaled(input, weight, degrees)                 # reuse_conv_kernel.cu:971
-    return [plan.aggregate(tmp, degrees, "gcn_prescaled", tiles="auto")]
+    tmp = _transform(input, weight)                                 # reuse_conv_kernel.cu:971
+    return [plan.aggregate(tmp, degrees, "gcn", tiles="auto")]
 
 
 def reuse_backward_v2(d_output, X, W, uniqpart_column_index, degrees, uniqpart_pointers, part2Node_ptr, part2Node_col,
@@ -213,5 +220,5 @@ def reuse_backward_v2(d_output, X, W, uniqpart_column_index, degrees, uniqpart_p
                  (part2Node_col, "part2Node_col")):
         _check_input(t, n)
     plan = plan_for_v2(d_output.size(0), uniqpart_column_index, uniqpart_pointers, part2Node_ptr, part2Node_col)
-    ds = scale_rows(d_output, degrees, "rsqrt")
-    return _backward_tail(plan.aggregate(ds, degrees, "gcn_prescaled", tiles="auto"), X, W)
+    ds, mode = _gcn_rows(d_output, degrees)
+    return _backward_tail(plan.aggregate(ds, degrees, mode, tiles="auto"), X, W)

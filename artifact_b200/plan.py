@@ -285,7 +285,7 @@ class AggregationPlan:
 
     def aggregate(self, x, degrees=None, mode="gcn", out=None, cache_result=None, workspace=None, phases=7,
                   accumulate=False, tiles=1, gather_events=None, bias=None, self_x=None, self_scale=1.0,
-                  relu=False):
+                  relu=False, _cache_rows=None):
         """out[v] = scale(v) * sum over v's gathered rows; see rof_aggregate() in include/rof_b200.h.
         `x` is [num_nodes, dim] fp32 on the GPU; returns a new [rows, dim] tensor unless `out` is given.
         tiles: 1 = one pass over the whole plan; N > 1 or "auto" = N source tiles (see auto_tiles).
@@ -293,17 +293,19 @@ class AggregationPlan:
         bias / self_x / self_scale / relu: fused epilogue out = act(result + self_scale * self_x + bias)
         (rof_aggregate_fused); self_x is [num_nodes, dim] indexed by global row id."""
         if tiles == "auto":
-            tiles = self.auto_tiles(x.size(1)) if (cache_result is None and phases == 7 and not accumulate) else 1
+            tiles = self.auto_tiles(x.size(1)) if (phases == 7 and not accumulate) else 1
         if tiles > 1:
-            if cache_result is not None or phases != 7 or accumulate:
-                raise RuntimeError("source tiling runs whole passes without a part_result_cache")
+            if phases != 7 or accumulate:
+                raise RuntimeError("source tiling runs whole passes")
             self.launches = 0
             plans = self.tile_plans(tiles)
             for k, p in enumerate(plans):
                 last = k + 1 == len(plans)                 # the epilogue belongs to the last tile only
-                out = p.aggregate(x, degrees, mode, out=out, workspace=workspace, accumulate=k > 0,
-                                  gather_events=gather_events, bias=bias if last else None,
-                                  self_x=self_x if last else None, self_scale=self_scale, relu=relu and last)
+                # every tile fills the rows of the part_result_cache whose groups it builds
+                out = p.aggregate(x, degrees, mode, out=out, cache_result=cache_result, workspace=workspace,
+                                  accumulate=k > 0, gather_events=gather_events, bias=bias if last else None,
+                                  self_x=self_x if last else None, self_scale=self_scale, relu=relu and last,
+                                  _cache_rows=self.info["num_groups"])
                 self.launches += p.launches
             return out
         if not x.is_cuda:
@@ -334,10 +336,11 @@ class AggregationPlan:
             deg_ptr = ctypes.c_void_p(degrees.data_ptr())
         cache_ptr = None
         if cache_result is not None:
+            cache_rows = i["num_groups"] if _cache_rows is None else _cache_rows
             if (not cache_result.is_cuda or cache_result.dtype != torch.float32 or not cache_result.is_contiguous()
-                    or tuple(cache_result.shape) != (i["num_groups"], dim + 1)):
+                    or tuple(cache_result.shape) != (cache_rows, dim + 1)):
                 raise RuntimeError(f"part_result_cache must be a contiguous float32 CUDA tensor of shape "
-                                   f"[{i['num_groups']}, {dim + 1}]")
+                                   f"[{cache_rows}, {dim + 1}]")
             cache_ptr = ctypes.c_void_p(cache_result.data_ptr())
         bias_ptr = self_ptr = None
         ld_self = 0

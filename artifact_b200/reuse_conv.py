@@ -167,6 +167,6 @@ class ROF_GCNConv(torch.nn.Module):
         else:
             raise NotImplementedError
         with torch.no_grad():
-            tmp = ROF._transform_scaled(x, self.weight, info.degrees)
-            return plan.aggregate(tmp, info.degrees, "gcn_prescaled", tiles="auto",
+            tmp = ROF._transform(x, self.weight)
+            return plan.aggregate(tmp, info.degrees, "gcn", tiles="auto",
                                   bias=self.bias.detach() if self.bias is not None else None, relu=relu)

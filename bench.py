@@ -329,6 +329,9 @@ class Job:
         v2 = [i32(L[k]) for k in ("uniqpart_column_index", "uniqpart_pointers", "part2Node_ptr", "part2Node_col")]
         self.plan = AggregationPlan.from_v2(n, *v2, rows=(self.r0, self.r1), device=dev)
         del v2
+        # the plan uses the groups only where they save enough gathered rows (rof_plan_create_v2)
+        self.ratios["groups_used_by_this_rank_s_plan"] = self.plan.info["num_groups"]
+        self.ratios["gathered_rows_of_this_rank_s_plan"] = self.plan.info["gather_entries"]
         self.plain = None
         if want_plain:
             self.plain = AggregationPlan.from_parts(n, i32(g.indices_src), i32(g.indptr_dst), i32(np.arange(n)),

@@ -185,7 +185,9 @@ int64_t rof_plan_algorithmic_bytes(const rof_plan* plan, int dim, int mode);
  *            exactly once (no zero-fill needed, no atomics)
  *   cache_result  optional [num_groups, dim+1] fp32 device: upstream's `part_result_cache`
  *            (ROF_v1 only); when given, phase A also stores each partial row and the 1.0
- *            "ready" flag there like upstream's caching kernel (:479-485).  May be NULL.
+ *            "ready" flag there like upstream's caching kernel (:479-485).  May be NULL.  A plan made
+ *            by rof_plan_create_stages*() fills the rows of the groups it builds, under the ids
+ *            those groups have in the plan it was split from: give every stage the same buffer.
  *   workspace / workspace_bytes  device scratch, see rof_plan_workspace_bytes()
  *
  * Work is only enqueued on `stream`; the call does not synchronise.

@@ -13,6 +13,11 @@ for p in (ROOT, os.path.join(ROOT, "oracle")):
 GOLDEN = os.path.join(ROOT, "tests", "golden")
 
 
+# The suite exercises the reuse machinery on every fixture: ROF_v2 plans keep every group the search
+# picked, also where the library's cost rule would inline them (test_plan_cpu.py tests the rule itself).
+os.environ.setdefault("ROF_REUSE_MIN", "0")
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
     # the CPU suite needs the native libraries too (host helpers, plan builder, oracle)

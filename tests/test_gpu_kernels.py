@@ -201,3 +201,34 @@ def test_shared_memory_tiles(name, dim, monkeypatch):
         xu = torch.from_numpy(np.pad(x, ((0, 0), (1, 0)))).to(DEV)[:, 1:]
         got = plan.aggregate(xu, deg, "sum")
         assert_close(got.cpu().numpy(), oracle_v2(L, deg_np, x, "sum"), what="unaligned rows")
+
+
+@pytest.mark.parametrize("name", ["c5_n1024_ps2", "c2_n640_ps2"])
+def test_v1_cache_mirror_with_source_tiles(name):
+    """ROF_v1 with the pass cut into source tiles: every tile fills the rows of the caller's
+    part_result_cache whose groups it builds (under their original ids), flag column included, and the
+    output equals the untiled pass"""
+    g = load_golden(name)
+    n, L = g["N"], g["layouts"]
+    plan = AggregationPlan.from_v1(n, *[dev_i32(a) for a in layout_args(L, "v1")])
+    G = plan.info["num_groups"]
+    assert G > 0
+    dim = 24
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((n, dim)).astype(np.float32)
+    deg_np = np.maximum(g["degrees"], 1.0)
+    xd, deg = torch.from_numpy(x).to(DEV), torch.from_numpy(deg_np).to(DEV)
+    c1 = torch.zeros((G, dim + 1), device=DEV)
+    c3 = torch.full((G, dim + 1), -7.0, device=DEV)
+    o1 = plan.aggregate(xd, deg, "gcn", cache_result=c1)
+    o3 = plan.aggregate(xd, deg, "gcn", cache_result=c3, tiles=3)
+    cache = np.zeros((G, dim + 1), np.float32)
+    want = rof_oracle.aggregate_v1(x, L["column_index"], deg_np, L["part_pointers"], L["part2Node"], cache,
+                                   L["part_cache_flagindex"], L["part_pointers_cache"], L["column_index_cache"],
+                                   "gcn", True)
+    assert_close(o1.cpu().numpy(), want, what="untiled")
+    assert_close(o3.cpu().numpy(), want, what="three source tiles")
+    assert (c3[:, dim] == 1.0).all() and (c1[:, dim] == 1.0).all()
+    assert_close(c3.cpu().numpy(), c1.cpu().numpy(), what="part_result_cache rows, tiled vs untiled")
+    with pytest.raises(RuntimeError):
+        plan.aggregate(xd, deg, "gcn", cache_result=torch.zeros((G + 1, dim + 1), device=DEV), tiles=3)

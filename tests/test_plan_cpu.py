@@ -246,3 +246,25 @@ def test_tiles_are_built_only_where_rows_share_entries(monkeypatch):
     assert AggregationPlan.from_v2(c2["N"], *layout_args(c2["layouts"], "v2")).info["num_tiles"] == 0
     monkeypatch.setenv("ROF_TILES", "0")
     assert AggregationPlan.from_v2(c5["N"], *layout_args(c5["layouts"], "v2")).info["num_tiles"] == 0
+
+
+def test_reuse_groups_are_used_only_where_they_pay(monkeypatch):
+    """the library's own rule (ROF_REUSE_MIN unset): the community fixture saves about a third of its
+    gathered rows and keeps its groups; the power-law fixture saves a few per cent and is run without
+    partial rows — same rows either way"""
+    from conftest import load_golden
+    monkeypatch.delenv("ROF_REUSE_MIN", raising=False)
+    c5, c2 = load_golden("c5_n1024_ps2"), load_golden("c2_n640_ps2")
+    p5 = AggregationPlan.from_v2(c5["N"], *layout_args(c5["layouts"], "v2"))
+    p2 = AggregationPlan.from_v2(c2["N"], *layout_args(c2["layouts"], "v2"))
+    assert p5.info["num_groups"] > 0 and p5.info["gather_entries"] < 0.8 * p5.info["original_edges"]
+    assert p2.info["num_groups"] == 0 and p2.info["gather_entries"] == p2.info["original_edges"]
+    for g, p in ((c5, p5), (c2, p2)):
+        rows = expand_rows(p.export(), g["N"])
+        ip, ix = g["indptr_dst"], g["indices_src"]
+        assert all(rows[v] == list(ix[ip[v]:ip[v + 1]]) for v in range(g["N"]))
+    # kept groups all have a positive benefit: fan-out x (size - 1) > size + 1
+    ex = p5.export()
+    fan = np.bincount(ex["col"][ex["col"] >= c5["N"]] - c5["N"], minlength=p5.info["num_groups"])
+    size = np.diff(ex["group_ptr"])
+    assert (fan * (size - 1) > size + 1).all()
