@@ -273,37 +273,52 @@ __device__ __forceinline__ void gather_batch(float (&acc)[C][VEC], int c, float 
   }
 }
 
-// acc += sum over col[begin, end) of (WEIGHTED ? rsqrt(degrees[c]) : 1) * row(c).  The group
-// fetches L entries at a time and walks them in batches of U rows; what is left of a window
-// is walked in batches of 4, 2 and 1, so that no load slot is issued for an entry that does
-// not exist (short rows are bound by instruction issue as much as by latency).
+// One window of a range: the group's lanes fetch up to L consecutive column entries (and, for GCN,
+// the weight of each feature row); lane l holds entry e + l.
+template <int L, bool WEIGHTED, bool MIXED>
+__device__ __forceinline__ void load_window(const int32_t* __restrict__ col, int e, int end, const RowSource& src,
+                                            const float* __restrict__ degrees, int lane, int& c, float& w) {
+  const int mine = e + lane;
+  c = 0;
+  w = 1.0f;
+  if (mine < end) {
+    c = __ldg(col + mine);
+    if constexpr (WEIGHTED) {
+      if (!MIXED || c < src.num_nodes) w = __frsqrt_rn(__ldg(degrees + c));
+    }
+    if constexpr (!MIXED) c -= src.c_offset;
+  }
+}
+
+// Adds the rows of the first `cnt` entries of a window in batches of U; what is left is walked in
+// batches of 4, 2 and 1, so that no load slot is issued for an entry that does not exist (short
+// rows are bound by instruction issue as much as by latency).
+template <int VEC, int L, int C, int U, bool WEIGHTED, bool MIXED>
+__device__ __forceinline__ void consume_window(float (&acc)[C][VEC], int c, float w, int cnt, const RowSource& src,
+                                               int lane, unsigned gmask, const bool (&active)[C]) {
+  int j = 0;
+  for (; j + U <= cnt; j += U) gather_batch<VEC, L, C, U, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane);
+  if constexpr (U > 4) {
+    if (cnt - j >= 4) { gather_batch<VEC, L, C, 4, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane); j += 4; }
+  }
+  if constexpr (U > 2) {
+    if (cnt - j >= 2) { gather_batch<VEC, L, C, 2, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane); j += 2; }
+  }
+  if constexpr (U > 1) {
+    if (cnt - j >= 1) gather_batch<VEC, L, C, 1, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane);
+  }
+}
+
+// acc += sum over col[begin, end) of (WEIGHTED ? rsqrt(degrees[c]) : 1) * row(c), window by window.
 template <int VEC, int L, int C, int U, bool WEIGHTED, bool MIXED>
 __device__ __forceinline__ void accumulate_range(float (&acc)[C][VEC], const int32_t* __restrict__ col, int begin,
                                                  int end, const RowSource& src, const float* __restrict__ degrees,
                                                  int lane, unsigned gmask, const bool (&active)[C]) {
   for (int e = begin; e < end; e += L) {
-    const int mine = e + lane;
-    int c = 0;
-    float w = 1.0f;
-    if (mine < end) {
-      c = __ldg(col + mine);
-      if constexpr (WEIGHTED) {
-        if (!MIXED || c < src.num_nodes) w = __frsqrt_rn(__ldg(degrees + c));
-      }
-      if constexpr (!MIXED) c -= src.c_offset;
-    }
-    const int cnt = min(L, end - e);
-    int j = 0;
-    for (; j + U <= cnt; j += U) gather_batch<VEC, L, C, U, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane);
-    if constexpr (U > 4) {
-      if (cnt - j >= 4) { gather_batch<VEC, L, C, 4, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane); j += 4; }
-    }
-    if constexpr (U > 2) {
-      if (cnt - j >= 2) { gather_batch<VEC, L, C, 2, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane); j += 2; }
-    }
-    if constexpr (U > 1) {
-      if (cnt - j >= 1) gather_batch<VEC, L, C, 1, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane);
-    }
+    int c;
+    float w;
+    load_window<L, WEIGHTED, MIXED>(col, e, end, src, degrees, lane, c, w);
+    consume_window<VEC, L, C, U, WEIGHTED, MIXED>(acc, c, w, min(L, end - e), src, lane, gmask, active);
   }
 }
 
@@ -606,11 +621,15 @@ __global__ void __launch_bounds__(256, (C <= 2 ? 4 : 2)) gather_tiles_kernel(con
 #pragma unroll
   for (int k = 0; k < C; ++k) active[k] = (lane + k * L) < nvec;
 
+  const RowSource gsrc{a.x + lane * 4, a.ldx, 0, a.partials + lane * 4, a.ldp, a.num_nodes};
+
   // this group's first item: fetched before the staging so that both latencies overlap
   int4 raw = make_int4(0, 0, 0, 0);
   if (group < num_items) raw = __ldg(reinterpret_cast<const int4*>(t.titems) + first_item + group);
 
-  // phase 1: stage the tile's shared rows
+  // phase 1: stage the tile's shared rows (weighted for GCN, so that the adds below need no multiply).
+  // Gathering the first item's private rows while the staged rows are on their way was tried and
+  // measured no faster (community graph, width 64: 0.67 vs 0.66 ms).
 #pragma unroll 2
   for (int s = group; s < stage_count; s += G) {
     const int c = __ldg(t.stage_col + stage_begin + s);
@@ -644,12 +663,9 @@ __global__ void __launch_bounds__(256, (C <= 2 ? 4 : 2)) gather_tiles_kernel(con
     for (int k = 0; k < C; ++k)
 #pragma unroll
       for (int q = 0; q < 4; ++q) acc[k][q] = 0.0f;
-
     // rows read from global memory (partial rows and feature rows, selected per entry)
-    if (end > mid) {
-      const RowSource src{a.x + lane * 4, a.ldx, 0, a.partials + lane * 4, a.ldp, a.num_nodes};
-      accumulate_range<4, L, C, U, WEIGHTED, true>(acc, t.tcol, mid, end, src, a.degrees, lane, gmask, active);
-    }
+    if (end > mid)
+      accumulate_range<4, L, C, U, WEIGHTED, true>(acc, t.tcol, mid, end, gsrc, a.degrees, lane, gmask, active);
     // rows staged in shared memory
     for (int e = begin; e < mid; e += L) {
       const int mine = e + lane;

@@ -230,7 +230,9 @@ class PipelinedAggregator:
             else:
                 self.stage_plans, self.transfer_of = stage_plans or [plan], [0]
         dev = f.full.device
-        self.comm_stream = torch.cuda.Stream(dev) if f.world > 1 else None
+        # the transfers run at high priority: their few blocks must get onto SMs that a gather kernel
+        # with hundreds of thousands of short blocks would otherwise keep full
+        self.comm_stream = torch.cuda.Stream(dev, priority=-1) if f.world > 1 else None
         self.ready = torch.cuda.Event() if f.world > 1 else None
         self.landed = [torch.cuda.Event() for _ in self.schedule]
         self.launches = 0

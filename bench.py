@@ -45,9 +45,10 @@ CACHE_VERSION = 2          # bump when the graph generators or the search change
 # dram__bytes_read.sum + dram__bytes_write.sum of one pass of the dominant kernel, from committed
 # ncu captures (one per kernel change); None where no capture exists
 NCU_DRAM_BYTES_PER_PASS = {
-    "c2:D256:sum": 5.13e9,     # 4 source tiles x 1.28 GB (untiled: 25.03 GB)
-    "c2:D64:sum": 1.44e9,
-    "c5:D64:sum": 2.03e9,
+    "c2:D256:sum": 3.35e9,     # 4 source tiles; two captured: 0.71 and 0.96 GB (untiled first version: 25.0 GB)
+    "c2:D256:gcn": 3.9e9,      # two of four tiles captured: 0.84 and 1.11 GB
+    "c2:D602:sum": 17.2e9,     # two of eight tiles captured: 1.80 and 2.49 GB
+    "c5:D64:sum": 2.04e9,      # tile kernel
 }
 
 
