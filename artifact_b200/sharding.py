@@ -152,21 +152,41 @@ def stage_schedule(world):
     return stages
 
 
-def compute_stages(blocks, rank, schedule, dim, entries_per_row, tile_bytes=64e6, min_entries_per_tile=48):
+def piece_rows(lo, hi, piece, pieces):
+    """rows of piece `piece` when [lo, hi) is cut into `pieces` contiguous parts of about equal size"""
+    n = hi - lo
+    return lo + n * piece // pieces, lo + n * (piece + 1) // pieces
+
+
+def transfer_pieces(world, received_bytes_per_pass, piece_bytes=256e6, max_pieces=4):
+    """How many pieces a peer group's transfer would be cut into if pieces of about `piece_bytes` were
+    wanted (PipelinedAggregator(pieces=...)).  Pieces let the aggregation of one piece cover the transfer
+    of the next: a large transfer beside a memory-bound gather is slowed down by it (2 B200s, 2.45M-node
+    graph, D=256: 1.25 GB arrive in 1.97 ms alone and in ~5.9 ms beside the gather), and a stage cannot
+    start before all it reads has landed.  But every piece is one more compute stage, i.e. one more
+    pass over every destination row, and on that graph (mean degree 50) this costs more than the overlap
+    returns: 19.8 / 21.0 / 23.7 ms per step with 1 / 2 / 4 pieces.  The pipeline therefore defaults to
+    one piece; this helper is for callers whose rows are long enough to afford more."""
+    if world <= 1:
+        return 1
+    groups = max(1, len(stage_schedule(world)) - 1)
+    return int(min(max_pieces, max(1, round(received_bytes_per_pass / groups / piece_bytes))))
+
+
+def compute_stages(ranges_per_stage, n, dim, entries_per_row, tile_bytes=64e6, min_entries_per_tile=48):
     """Cuts every transfer stage into compute stages whose source rows fit L2.
 
-    -> (range_bounds, stage_of_range, transfer_stage_of_compute_stage).  Transfer stage s brings the
-    blocks of ranks (rank + k) % world, k in schedule[s]; when those blocks hold more than
-    `tile_bytes` of features the stage's rows are cut into tiles (contiguous row ranges of about
-    equal size) that are aggregated one after the other, so that the gathers of a tile hit L2
-    (126 MB) — unless a destination would then gather fewer than `min_entries_per_tile` rows per
-    tile, where the extra passes over the output cost more than the misses."""
-    world = len(blocks)
-    n = blocks[-1][1]
+    ranges_per_stage[s]: the feature-row ranges [(r0, r1), ...] that transfer stage s makes readable
+    (stage 0: the rank's own block).  -> (range_bounds, stage_of_range,
+    transfer_stage_of_compute_stage).  When a stage's rows hold more than `tile_bytes` of features
+    they are cut into tiles (contiguous row ranges of about equal size) that are aggregated one after
+    the other, so that the gathers of a tile hit L2 (126 MB) — unless a destination would then gather
+    fewer than `min_entries_per_tile` rows per tile, where the extra passes over the output cost more
+    than the misses."""
     pieces = []                       # (r0, r1, compute stage)
     transfer_of = []
-    for s, offs in enumerate(schedule):
-        rng = sorted(blocks[(rank + k) % world] for k in offs)
+    for s, ranges in enumerate(ranges_per_stage):
+        rng = sorted((int(a), int(b)) for a, b in ranges if b > a)
         rows = sum(b - a for a, b in rng)
         tiles = 1
         if rows > 0:
@@ -187,14 +207,12 @@ def compute_stages(blocks, rank, schedule, dim, entries_per_row, tile_bytes=64e6
     pieces.sort()
     bounds, stage_of = [0], []
     for a, b, k in pieces:
-        if a == b:
-            continue
         if a != bounds[-1]:
-            raise RuntimeError("blocks do not tile the rows")
+            raise RuntimeError("the stages' ranges do not tile the rows")
         bounds.append(b)
         stage_of.append(k)
     if bounds[-1] != n:
-        raise RuntimeError("blocks do not cover every row")
+        raise RuntimeError("the stages' ranges do not cover every row")
     return bounds, stage_of, transfer_of
 
 
@@ -202,30 +220,48 @@ class PipelinedAggregator:
     """All-gather overlapped with aggregation, stage by stage.
 
     Rank r reads its own block in stage 0 and the blocks of ranks (r + k) % world, k in the
-    stage's offsets (see stage_schedule), in the later stages.  Each stage's blocks travel as one
-    group of paired sends/receives on a side stream (send the own block to rank r-k, receive the
-    block of rank r+k; NVSwitch gives every pair full bandwidth), and the per-stage plans run on
-    the compute stream as soon as their blocks have landed, adding into `out`.  A transfer stage
-    whose blocks exceed L2 is aggregated as several compute stages (compute_stages).  The result
-    equals the whole-plan aggregate up to the order of the fp32 adds.  Every kernel reads this
-    GPU's memory only.
+    stage's offsets (see stage_schedule), in the later stages; with `pieces` > 1 each group's transfer
+    is cut further into that many stages (see transfer_pieces for when that pays).  A stage's rows travel as one group of paired
+    sends/receives on a high-priority side stream (send a piece of the own block to rank r-k, receive
+    the same piece of the block of rank r+k; NVSwitch gives every pair full bandwidth), and the
+    per-stage plans run on the compute stream as soon as their rows have landed, adding into `out`.
+    A stage whose rows exceed L2 is aggregated as several compute stages (compute_stages).  The result
+    equals the whole-plan aggregate up to the order of the fp32 adds.  Every kernel reads this GPU's
+    memory only.
     """
 
     def __init__(self, plan, features: ShardedFeatures, stage_plans=None, schedule=None, tile_bytes=64e6,
-                 like=None):
+                 like=None, pieces=None):
         f = features
         r0, r1 = f.blocks[f.rank]
         if (plan.info["row_begin"], plan.info["row_end"]) != (r0, r1):
             raise RuntimeError("the plan does not cover this rank's row block")
         self.features, self.whole = f, plan
         if like is not None:          # a second feature buffer over the same plans (e.g. the gradient's)
-            self.schedule, self.stage_plans, self.transfer_of = like.schedule, like.stage_plans, like.transfer_of
+            self.schedule, self.pieces, self.transfers = like.schedule, like.pieces, like.transfers
+            self.stage_plans, self.transfer_of = like.stage_plans, like.transfer_of
         else:
             self.schedule = schedule or stage_schedule(f.world)
+            self.pieces = max(1, int(pieces or 1))
+            # transfer stages: the own block, then every group of peers, piece by piece
+            self.transfers = []
+            for offs in self.schedule:
+                if all(k % f.world == 0 for k in offs):
+                    self.transfers.append([(k, 0, 1) for k in offs])
+                else:
+                    for pc in range(self.pieces):
+                        self.transfers.append([(k, pc, self.pieces) for k in offs])
             if f.world > 1:
                 rows = max(r1 - r0, 1)
+                ranges = []
+                for st in self.transfers:
+                    rs = []
+                    for k, pc, npc in st:
+                        lo, hi = piece_rows(*f._block_rows((f.rank + k) % f.world), pc, npc)
+                        rs.append((min(lo, f.n), min(hi, f.n)))       # padding rows hold no features
+                    ranges.append(rs)
                 bounds, stage_of, self.transfer_of = compute_stages(
-                    f.blocks, f.rank, self.schedule, f.dim, plan.info["gather_entries"] / rows, tile_bytes)
+                    ranges, f.n, f.dim, plan.info["gather_entries"] / rows, tile_bytes)
                 self.stage_plans = stage_plans or plan.stages_by_ranges(bounds, stage_of)
             else:
                 self.stage_plans, self.transfer_of = stage_plans or [plan], [0]
@@ -234,16 +270,30 @@ class PipelinedAggregator:
         # with hundreds of thousands of short blocks would otherwise keep full
         self.comm_stream = torch.cuda.Stream(dev, priority=-1) if f.world > 1 else None
         self.ready = torch.cuda.Event() if f.world > 1 else None
-        self.landed = [torch.cuda.Event() for _ in self.schedule]
+        self.landed = [torch.cuda.Event() for _ in self.transfers]
         self.launches = 0
 
-    def _transfer(self, cur):
+    def _stage_ops(self, stage):
         f = self.features
+        ops = []
+        for k, pc, npc in stage:
+            if k % f.world == 0:
+                continue                                  # the rank's own block is already in place
+            src, dst = (f.rank + k) % f.world, (f.rank - k) % f.world
+            s0, s1 = piece_rows(*f._block_rows(f.rank), pc, npc)
+            d0, d1 = piece_rows(*f._block_rows(src), pc, npc)
+            if s1 > s0:
+                ops.append(dist.P2POp(dist.isend, f._store[s0:s1], dst, group=f.group))
+            if d1 > d0:
+                ops.append(dist.P2POp(dist.irecv, f._store[d0:d1], src, group=f.group))
+        return ops
+
+    def _transfer(self, cur):
         self.ready.record(cur)
         with torch.cuda.stream(self.comm_stream):
             self.comm_stream.wait_event(self.ready)
-            for s, offs in enumerate(self.schedule):
-                ops = f.exchange_ops(offs)
+            for s, stage in enumerate(self.transfers):
+                ops = self._stage_ops(stage)
                 if ops:
                     for w in dist.batch_isend_irecv(ops):
                         w.wait()
@@ -256,7 +306,7 @@ class PipelinedAggregator:
         waited = set()
         for k, p in enumerate(self.stage_plans):
             s = self.transfer_of[k]
-            if wait and f.world > 1 and s not in waited and any(o % f.world for o in self.schedule[s]):
+            if wait and f.world > 1 and s not in waited and any(o % f.world for o, _, _ in self.transfers[s]):
                 cur.wait_event(self.landed[s])
                 waited.add(s)
             p.aggregate(x_full, degrees, mode, out=out, accumulate=k > 0)

@@ -354,9 +354,10 @@ class Job:
         self.pipes = {}
         if pipelined:
             sched = [[int(k) for k in st.split(",")] for st in ns.schedule.split("|")] if ns.schedule else None
-            px = PipelinedAggregator(self.plan, self.feat_x, schedule=sched)
+            px = PipelinedAggregator(self.plan, self.feat_x, schedule=sched, pieces=getattr(ns, "pieces", 0) or None)
             self.pipes = {id(self.feat_x): px, id(self.feat_g): PipelinedAggregator(self.plan, self.feat_g, like=px)}
-            self.stage_info = {"transfer_stages": px.schedule, "compute_stages": len(px.stage_plans)}
+            self.stage_info = {"peer_groups": px.schedule, "pieces_per_group": px.pieces,
+                               "transfer_stages": len(px.transfers), "compute_stages": len(px.stage_plans)}
         self.t_plan = time.time() - t0
         self.launches = 0
         self.gather_events = []
@@ -617,7 +618,7 @@ def side_config(name, args, rank, world, dev, steps):
     """ms per step and check of another benchmark configuration, with the same machinery"""
     d, ps, mode = WORKLOADS[name]
     ns = argparse.Namespace(**vars(args))
-    ns.workload, ns.dim, ns.part_size, ns.mode, ns.tiles, ns.schedule = name, d, ps, mode, "auto", ""
+    ns.workload, ns.dim, ns.part_size, ns.mode, ns.tiles, ns.schedule, ns.pieces = name, d, ps, mode, "auto", "", 0
     job = Job(ns, rank, world, dev, want_plain=(world == 1))
     try:
         ms, _, _ = job.timed(job.plan, steps, 3)
@@ -655,6 +656,7 @@ def main():
     ap.add_argument("--no-pipeline", dest="pipeline", action="store_false",
                     help="N > 1: one all-gather, then the aggregation (no overlap)")
     ap.add_argument("--schedule", default="", help="N > 1 pipeline stages as ring offsets, e.g. '0|1,2,3|4,5,6,7'")
+    ap.add_argument("--pieces", type=int, default=0, help="N > 1: pieces each peer group's transfer is cut into (0: by size)")
     ap.add_argument("--tiles", default="auto", help="source tiles per pass on one GPU: auto or an integer")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")

@@ -52,3 +52,23 @@ def test_header_is_plain_c(tmp_path):
                            "-L", libdir, "-lrof_b200", f"-Wl,-rpath,{libdir}", "-Wl,-rpath,/usr/local/cuda/lib64"])
     out = subprocess.run([str(exe)], capture_output=True, text=True)
     assert out.returncode == 0 and out.stdout.split() == [str(len(names)), "100"]
+
+
+def test_argument_checks_of_the_auxiliary_entry_points():
+    """bad arguments come back as status codes before anything touches a device"""
+    import ctypes
+    lib = _native.cuda()
+    buf = (ctypes.c_float * 64)()
+    p = ctypes.cast(buf, ctypes.c_void_p)
+    assert lib.rof_scale_rows(None, 8, 8, None, 0, p, 8, 4, None) == 1            # null x
+    assert lib.rof_scale_rows(p, 4, 8, None, 0, p, 8, 4, None) == 1               # ldx < dim
+    assert lib.rof_scale_rows(p, 8, 8, None, 1, p, 8, 4, None) == 1               # rsqrt without degrees
+    assert lib.rof_scale_rows(p, 8, 8, None, 7, p, 8, 4, None) == 1               # unknown op
+    assert lib.rof_scale_rows(p, 8, 8, None, 0, p, 8, 0, None) == 0               # nothing to do
+    assert b"rof_scale_rows" in lib.rof_last_error()
+    assert lib.rof_probe_read(None, 1024, 1, p, None) == 1
+    assert lib.rof_probe_read(ctypes.c_void_p(p.value + 4), 1024, 1, p, None) == 1   # not 16-byte aligned
+    assert lib.rof_plan_take_status(None) == 0
+    assert lib.rof_plan_export_tiles(None, None, None, None, None) == 1
+    handles = (ctypes.c_void_p * 2)()
+    assert lib.rof_plan_create_stages_ranges(None, None, None, 0, 0, handles, None) == 1

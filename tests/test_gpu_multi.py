@@ -58,7 +58,7 @@ def _worker(rank, world, port, name, q):
         feats_b.local_view().copy_(torch.from_numpy(x[b0:b1]).to(dev))
         plan_b = AggregationPlan.from_v2(n, *[i32(a_) for a_ in layout_args(g["layouts"], "v2")], rows=(b0, b1))
         out3 = torch.empty((b1 - b0, dim), device=dev)
-        pipe3 = PipelinedAggregator(plan_b, feats_b, tile_bytes=n * dim * 4 / 6)
+        pipe3 = PipelinedAggregator(plan_b, feats_b, tile_bytes=n * dim * 4 / 6, pieces=3)
         for _ in range(2):
             pipe3.aggregate(None, deg, mode, out3)
         torch.cuda.synchronize()
@@ -103,7 +103,7 @@ def test_sharded_and_pipelined_match_oracle(name):
         piped2 = np.concatenate([r[mode][2] for _, r in sorted(gathered, key=lambda t: t[0])])
         assert_close(piped2, want, what=f"pipelined, two half stages, {mode}")
         piped3 = np.concatenate([o for _, o in sorted((r[mode][3] for _, r in gathered), key=lambda t: t[0])])
-        assert_close(piped3, want, what=f"pipelined, blocks of equal work, tiled stages, {mode}")
+        assert_close(piped3, want, what=f"pipelined, blocks of equal work, transfers in 3 pieces, tiled stages, {mode}")
 
 
 def test_static_scratch_entry_point_on_a_second_device():

@@ -66,7 +66,8 @@ def test_compute_stages_tile_the_transfer_stages(name, world, rank):
     sched = stage_schedule(world)
     dim = 5
     # a tiny "L2" so that stages really are cut, and no minimum of entries per tile
-    bounds, stage_of, transfer_of = compute_stages(blocks, rank, sched, dim, 1e9, tile_bytes=n * dim * 4 / 5,
+    ranges = [[blocks[(rank + k) % world] for k in offs] for offs in sched]
+    bounds, stage_of, transfer_of = compute_stages(ranges, n, dim, 1e9, tile_bytes=n * dim * 4 / 5,
                                                    min_entries_per_tile=0)
     assert bounds[0] == 0 and bounds[-1] == n and all(a < b for a, b in zip(bounds, bounds[1:]))
     assert len(transfer_of) == max(stage_of) + 1 > len(sched)
@@ -91,8 +92,20 @@ def test_compute_stages_tile_the_transfer_stages(name, world, rank):
         got += eval_plan_numpy(ex, x, n)
     assert np.allclose(got, want, rtol=1e-9, atol=1e-9)
     # default tile size and the real minimum: these small graphs need no cut
-    b2, s2, t2 = compute_stages(blocks, rank, sched, dim, whole.info["gather_entries"] / max(r1 - r0, 1))
+    b2, s2, t2 = compute_stages(ranges, n, dim, whole.info["gather_entries"] / max(r1 - r0, 1))
     assert t2 == list(range(len(sched)))
+
+
+def test_transfer_pieces_follow_the_bytes():
+    from artifact_b200.sharding import piece_rows, transfer_pieces
+    assert transfer_pieces(1, 1e12) == 1
+    assert transfer_pieces(2, 119e6) == 1 and transfer_pieces(8, 208e6) == 1      # small transfers stay whole
+    assert transfer_pieces(2, 1.25e9) == 4 and transfer_pieces(8, 2.19e9) == 4     # large ones are cut (capped)
+    for lo, hi in ((0, 10), (7, 7), (100, 1003)):
+        for pcs in (1, 3, 4):
+            cuts = [piece_rows(lo, hi, p, pcs) for p in range(pcs)]
+            assert cuts[0][0] == lo and cuts[-1][1] == hi
+            assert all(a[1] == b[0] for a, b in zip(cuts, cuts[1:]))
 
 
 def test_stage_ranges_are_checked():
