@@ -31,14 +31,10 @@ inline bool fuse_reduce_enabled() {
   return v;
 }
 
-// Host policy for the gather kernels (see kernels.cu): the lane-group kernel.  The shared-memory
-// ring kernel measured about half as fast on B200 at every width tried (one bulk copy per row
-// of at most a few KB does not keep the copy engine busy) and is only used on request
-// (ROF_KERNEL=ring).
-inline int kernel_for(int num_items, int64_t entries) {
-  (void)num_items; (void)entries;
-  return 0;
-}
+// Host policy for the gather kernels (see kernels.cu): the lane-group kernel (0).  The shared-memory
+// ring kernel (1) measured about half as fast on B200 at every width tried (one bulk copy per row of
+// at most a few KB does not keep the copy engine busy) and only runs on request (ROF_KERNEL=ring).
+constexpr int kDefaultGatherKernel = 0;
 
 inline bool use_fine_cut(const rof_plan* p, int dim) { return p->fine.num_items > 0 && dim <= rof::kNarrowRowFloats; }
 
@@ -152,7 +148,7 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
     a.mirror = cache_result; a.ldm = (int64_t)dim + 1; a.mirror_flag_col = cache_result ? dim : -1;
     a.mirror_ids = p->d_group_orig;
     a.num_nodes = p->num_nodes; a.row_begin = 0; a.dim = dim; a.weight_gcn = gcn; a.scale_mode = 0;
-    a.out_padded = 1; a.kernel = kernel_for(p->num_groups, p->group_sources); a.status = p->d_status;
+    a.out_padded = 1; a.kernel = kDefaultGatherKernel; a.status = p->d_status;
     e = launch_gather(a, stream, &g_last_launches);
     if (e != cudaSuccess) return cuda_fail(e, "phase A (group partial sums)");
   }
@@ -165,7 +161,7 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
     a.num_nodes = p->num_nodes; a.row_begin = p->row_begin; a.dim = dim; a.weight_gcn = gcn; a.scale_mode = scale_mode;
     a.accumulate = accumulate;
     a.ep = ep;
-    a.kernel = kernel_for(num_items, p->gather_entries); a.status = p->d_status;
+    a.kernel = kDefaultGatherKernel; a.status = p->d_status;
     // short rows that share entries: staged once per tile in shared memory; the other items
     // (long rows, segments of split rows) follow with the lane-group kernel
     const bool tiled = p->tiled.num_tiles > 0 && tiles_supported(a);
@@ -175,7 +171,7 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
       if (e != cudaSuccess) return cuda_fail(e, "phase B (shared-memory tiles)");
       a.items = fine ? p->tiled.d_rest_items_fine : p->tiled.d_rest_items;
       a.num_items = fine ? p->tiled.num_rest_fine : p->tiled.num_rest;
-      a.kernel = 0;
+      a.kernel = kDefaultGatherKernel;
     }
     // when the caller wants the whole pass, the last segment of a split row to arrive finishes it
     if (num_split > 0 && (phases & ROF_PHASE_REDUCE) && fuse_reduce_enabled()) {

@@ -239,7 +239,7 @@ struct RowSource {
 // entries that exist.
 template <int VEC, int L, int C, int UU, bool WEIGHTED, bool MIXED>
 __device__ __forceinline__ void gather_batch(float (&acc)[C][VEC], int c, float w, int j, const RowSource& src,
-                                             unsigned gmask, const bool (&active)[C], int lane_vec0) {
+                                             unsigned gmask, const bool (&active)[C]) {
   float v[UU][C][VEC];
 #pragma unroll
   for (int u = 0; u < UU; ++u) {
@@ -259,7 +259,6 @@ __device__ __forceinline__ void gather_batch(float (&acc)[C][VEC], int c, float 
       }
     }
   }
-  (void)lane_vec0;
 #pragma unroll
   for (int u = 0; u < UU; ++u) {
     if constexpr (WEIGHTED) {
@@ -297,15 +296,15 @@ template <int VEC, int L, int C, int U, bool WEIGHTED, bool MIXED>
 __device__ __forceinline__ void consume_window(float (&acc)[C][VEC], int c, float w, int cnt, const RowSource& src,
                                                int lane, unsigned gmask, const bool (&active)[C]) {
   int j = 0;
-  for (; j + U <= cnt; j += U) gather_batch<VEC, L, C, U, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane);
+  for (; j + U <= cnt; j += U) gather_batch<VEC, L, C, U, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active);
   if constexpr (U > 4) {
-    if (cnt - j >= 4) { gather_batch<VEC, L, C, 4, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane); j += 4; }
+    if (cnt - j >= 4) { gather_batch<VEC, L, C, 4, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active); j += 4; }
   }
   if constexpr (U > 2) {
-    if (cnt - j >= 2) { gather_batch<VEC, L, C, 2, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane); j += 2; }
+    if (cnt - j >= 2) { gather_batch<VEC, L, C, 2, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active); j += 2; }
   }
   if constexpr (U > 1) {
-    if (cnt - j >= 1) gather_batch<VEC, L, C, 1, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active, lane);
+    if (cnt - j >= 1) gather_batch<VEC, L, C, 1, WEIGHTED, MIXED>(acc, c, w, j, src, gmask, active);
   }
 }
 

@@ -424,6 +424,25 @@ class AggregationPlan:
                 ctypes.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)))
         return out
 
+    def prepared_call(self, x, degrees, mode, out, accumulate):
+        """-> (function, argument list) of the C-ABI call that `aggregate(x, degrees, mode, out=out,
+        accumulate=accumulate)` makes, for callers that repeat the very same pass many times and have
+        validated it once through `aggregate` (the multi-GPU pipeline: several small launches per pass, where
+        the Python-side checks would otherwise be a visible share of the pass).  The last list entry is the
+        stream; the caller sets it before every call.  The tensors must outlive the prepared call."""
+        dim = x.size(1)
+        rows = self.info["row_end"] - self.info["row_begin"]
+        need = self.workspace_bytes(dim)
+        ws = self._get_workspace(need, x.device) if need else None
+        m = MODES[mode]
+        args = [self._h, 7 | (8 if accumulate else 0), m, ctypes.c_void_p(x.data_ptr()),
+                x.stride(0) if x.size(0) > 1 else dim, dim,
+                ctypes.c_void_p(degrees.data_ptr()) if (degrees is not None and m != MODES["sum"]) else None,
+                ctypes.c_void_p(out.data_ptr()), out.stride(0) if rows > 1 else dim, None,
+                ctypes.c_void_p(ws.data_ptr()) if ws is not None else None, ws.numel() if ws is not None else 0,
+                None, None, 0, ctypes.c_float(0.0), 0, None]
+        return _native.cuda().rof_aggregate_fused, args
+
     def last_launch_count(self):
         return self.launches
 

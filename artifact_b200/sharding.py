@@ -6,9 +6,13 @@ its block of rows and receives all the others (NCCL over NVLink) into a full [N,
 own HBM.  Kernels only ever read local memory.  Upstream is single-GPU (no collective anywhere in
 its tree); this module is new.
 """
+import ctypes
+
 import numpy as np
 import torch
 import torch.distributed as dist
+
+from . import _native
 
 
 def row_blocks(num_nodes, world, indptr=None, row_cost=8):
@@ -272,6 +276,7 @@ class PipelinedAggregator:
         self.ready = torch.cuda.Event() if f.world > 1 else None
         self.landed = [torch.cuda.Event() for _ in self.transfers]
         self.launches = 0
+        self._prepared = None          # (key, [(fn, args)] per compute stage) of the last validated pass
 
     def _stage_ops(self, stage):
         f = self.features
@@ -302,15 +307,31 @@ class PipelinedAggregator:
     def _compute(self, cur, degrees, mode, out, wait=True):
         f = self.features
         x_full = f.full[:f.n]
-        self.launches = 0
+        # a pass is several small launches: after the first, fully checked pass over the same buffers the
+        # stages are re-issued through prepared C-ABI calls, without the Python-side checks
+        key = (x_full.data_ptr(), out.data_ptr(), tuple(out.shape), out.stride(0),
+               degrees.data_ptr() if degrees is not None else 0, mode)
+        fast = self._prepared[1] if (self._prepared is not None and self._prepared[0] == key) else None
+        launches = 0
         waited = set()
+        prepared = []
         for k, p in enumerate(self.stage_plans):
             s = self.transfer_of[k]
             if wait and f.world > 1 and s not in waited and any(o % f.world for o, _, _ in self.transfers[s]):
                 cur.wait_event(self.landed[s])
                 waited.add(s)
-            p.aggregate(x_full, degrees, mode, out=out, accumulate=k > 0)
-            self.launches += p.last_launch_count()
+            if fast is not None:
+                fn, args = fast[k]
+                args[-1] = ctypes.c_void_p(cur.cuda_stream)
+                with torch.cuda.device(f.full.device):
+                    _native.check(fn(*args))
+            else:
+                p.aggregate(x_full, degrees, mode, out=out, accumulate=k > 0)
+                launches += p.last_launch_count()
+                prepared.append(p.prepared_call(x_full, degrees, mode, out, k > 0))
+        if fast is None:
+            self.launches = launches
+            self._prepared = (key, prepared)
         return out
 
     def aggregate(self, x_local, degrees, mode, out):
