@@ -278,7 +278,13 @@ static int finalize_plan_impl(HostPlan& hp, rof_plan** out, cudaStream_t stream)
 #pragma omp parallel for schedule(static, 1024)
   for (int r = 0; r < rows; ++r) {
     auto b = hp.col.begin() + hp.row_ptr[r], e = hp.col.begin() + hp.row_ptr[r + 1];
-    row_mid[(size_t)r] = std::stable_partition(b, e, [n_nodes](int32_t c) { return c >= n_nodes; }) - hp.col.begin();
+    auto m = std::stable_partition(b, e, [n_nodes](int32_t c) { return c >= n_nodes; });
+    row_mid[(size_t)r] = m - hp.col.begin();
+    // ascending ids inside each range: the reorganised layouts list a row's group sources first, and rows
+    // that sweep the feature matrix in the same direction share more cache lines (114.6M-edge graph, D=256:
+    // 11.9 ms per step in layout order, 11.4 ms sorted)
+    std::sort(b, m);
+    std::sort(m, e);
   }
   for (int r = 0; r < rows; ++r) p->partial_entries += row_mid[(size_t)r] - hp.row_ptr[r];
 
