@@ -356,3 +356,309 @@ class PipelinedAggregator:
     def aggregate_only(self, degrees, mode, out):
         """the pass's kernels over whatever the buffer holds, without transfers (timing breakdown)"""
         return self._compute(torch.cuda.current_stream(self.features.full.device), degrees, mode, out, wait=False)
+
+
+def column_chunks(dim, chunks=None):
+    """[(c0, c1)] column ranges a feature matrix of width `dim` is exchanged in.  Default: four chunks
+    from 256 floats, two from 128, one below (chunks narrower than 64 floats cost more in the gather
+    than the overlap returns); chunk widths are multiples of 4 floats except possibly the last."""
+    if chunks is None:
+        chunks = 4 if dim >= 256 else (2 if dim >= 128 else 1)
+    chunks = max(1, min(int(chunks), max(1, dim // 4)))
+    per = ((dim + chunks - 1) // chunks + 3) // 4 * 4
+    out = []
+    c = 0
+    while c < dim:
+        out.append((c, min(dim, c + per)))
+        c += per
+    return out
+
+
+class ColumnChunkedFeatures:
+    """A feature matrix stored as K column chunks, each a contiguous [world*block, width_k] buffer of its
+    own, so that every chunk is exchanged by ONE all_gather_into_tensor and can be aggregated (into the
+    matching columns of the output) while the next chunk is still travelling.  Row blocks are of equal
+    size (the collective needs that); rows are padded to a multiple of 4 floats."""
+
+    def __init__(self, num_nodes, dim, rank, world, device, chunks=None, dtype=torch.float32, group=None):
+        self.n, self.dim, self.rank, self.world, self.group = num_nodes, dim, rank, world, group
+        self.block, self.blocks = row_blocks(num_nodes, world)
+        self.cols = column_chunks(dim, chunks)
+        self._stores = [torch.zeros((self.block * world, (c1 - c0 + 3) // 4 * 4), dtype=dtype, device=device)
+                        for c0, c1 in self.cols]
+        self.device = self._stores[0].device
+
+    def chunk_full(self, k):
+        """[N, width_k] view of chunk k holding every rank's rows (valid after its all-gather)"""
+        c0, c1 = self.cols[k]
+        return self._stores[k][:self.n, :c1 - c0]
+
+    def chunk_local(self, k):
+        """this rank's [block, width_k] rows of chunk k (padding rows beyond N included)"""
+        c0, c1 = self.cols[k]
+        return self._stores[k][self.rank * self.block:(self.rank + 1) * self.block, :c1 - c0]
+
+    def _local_store(self, k):
+        return self._stores[k][self.rank * self.block:(self.rank + 1) * self.block]
+
+    def set_local(self, x_local):
+        """copy this rank's [rows <= block, dim] features into the chunk buffers"""
+        rows = x_local.size(0)
+        for k, (c0, c1) in enumerate(self.cols):
+            self.chunk_local(k)[:rows].copy_(x_local[:, c0:c1])
+
+    def fill_normal_(self, generator):
+        for s in self._stores:
+            s.normal_(generator=generator)
+
+    def rows(self, index):
+        """the full-width rows `index` (a LongTensor on this device) gathered from the chunks"""
+        return torch.cat([self.chunk_full(k)[index] for k in range(len(self.cols))], dim=1)
+
+    def all_gather_chunk(self, k):
+        if self.world > 1:
+            dist.all_gather_into_tensor(self._stores[k], self._local_store(k), group=self.group)
+
+
+class ColumnPipelinedAggregator:
+    """All-gather overlapped with aggregation, column chunk by column chunk.
+
+    The features travel as K column chunks, one all_gather_into_tensor each, on a high-priority side
+    stream; chunk k is aggregated — the whole block plan over a [N, width_k] matrix, writing columns
+    [c0, c1) of `out` — as soon as it has landed, while chunk k+1 is still on its way.  Compared with
+    staging by source block (PipelinedAggregator) nothing is added to an existing output row and no
+    destination row is visited once per stage with a fraction of its entries: a chunk re-reads only
+    the 4-byte column entries, so short rows keep their efficiency, the transfers are plain collectives
+    (one NCCL call each, in-network replication where NCCL uses it), and a chunk of up to ~64 MB needs
+    no source tiling to stay in L2.  Every kernel reads this GPU's memory only.
+    """
+
+    def __init__(self, plan, features: ColumnChunkedFeatures):
+        f = features
+        r0, r1 = f.blocks[f.rank]
+        if (plan.info["row_begin"], plan.info["row_end"]) != (r0, r1):
+            raise RuntimeError("the plan does not cover this rank's row block")
+        self.plan, self.features = plan, f
+        self.comm_stream = torch.cuda.Stream(f.device, priority=-1) if f.world > 1 else None
+        self.ready = torch.cuda.Event() if f.world > 1 else None
+        self.landed = [torch.cuda.Event() for _ in f.cols]
+        self.tiles = [plan.auto_tiles(c1 - c0) for c0, c1 in f.cols]
+        self.launches = 0
+
+    def _transfer(self, cur):
+        f = self.features
+        self.ready.record(cur)
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(self.ready)
+            for k in range(len(f.cols)):
+                f.all_gather_chunk(k)
+                self.landed[k].record(self.comm_stream)
+
+    def _compute(self, cur, degrees, mode, out, wait=True):
+        f = self.features
+        self.launches = 0
+        for k, (c0, c1) in enumerate(f.cols):
+            if wait and f.world > 1:
+                cur.wait_event(self.landed[k])
+            self.plan.aggregate(f.chunk_full(k), degrees, mode, out=out[:, c0:c1], tiles=self.tiles[k])
+            self.launches += self.plan.last_launch_count()
+        return out
+
+    def aggregate(self, x_local, degrees, mode, out):
+        f = self.features
+        cur = torch.cuda.current_stream(f.device)
+        if x_local is not None:
+            f.set_local(x_local)
+        if f.world > 1:
+            self._transfer(cur)
+        return self._compute(cur, degrees, mode, out)
+
+    def transfer_only(self):
+        """the pass's transfers without its kernels (timing breakdown); the current stream waits for them"""
+        if self.features.world <= 1:
+            return
+        cur = torch.cuda.current_stream(self.features.device)
+        self._transfer(cur)
+        for ev in self.landed:
+            cur.wait_event(ev)
+
+    def aggregate_only(self, degrees, mode, out):
+        """the pass's kernels over whatever the buffers hold, without transfers (timing breakdown)"""
+        return self._compute(torch.cuda.current_stream(self.features.device), degrees, mode, out, wait=False)
+
+
+class PieceMajorFeatures:
+    """A feature matrix stored piece-major: every rank's row block is cut into P pieces of `pb` rows, and
+    buffer piece p holds piece p of every rank — rows [p*world*pb, (p+1)*world*pb) of one [P*world*pb, D]
+    matrix — so that ONE all_gather_into_tensor per piece moves a P-th of every block into place, and
+    the pieces are exactly the source tiles the single-GPU pass walks (an L2-sized slice of the matrix
+    each).  Global row r of rank b (offset o = r - b*block inside its block) lives in buffer row
+    (o // pb) * world*pb + b*pb + o % pb; `perm` maps global ids to buffer rows, and a plan for this
+    layout is built from index tensors whose *source* ids went through it (PieceMajorPipeline.plan_from_v2).
+    Rows are padded to a multiple of 4 floats."""
+
+    def __init__(self, num_nodes, dim, rank, world, device, pieces, dtype=torch.float32, group=None):
+        self.n, self.dim, self.rank, self.world, self.group = num_nodes, dim, rank, world, group
+        self.pieces = max(1, int(pieces))
+        self.block, self.blocks = row_blocks(num_nodes, world)
+        self.pb = (self.block + self.pieces - 1) // self.pieces          # rows of one rank's piece
+        self.size = self.pieces * world * self.pb                         # rows of the buffer (>= num_nodes)
+        self._store = torch.zeros((self.size, (dim + 3) // 4 * 4), dtype=dtype, device=device)
+        self.full = self._store[:, :dim]
+        self.device = self._store.device
+
+    def perm(self, ids):
+        """buffer rows of global row ids (numpy array or LongTensor in, same kind out)"""
+        if isinstance(ids, torch.Tensor):
+            b = torch.div(ids, self.block, rounding_mode="floor")
+            o = ids - b * self.block
+            return torch.div(o, self.pb, rounding_mode="floor") * (self.world * self.pb) + b * self.pb + o % self.pb
+        ids = np.asarray(ids, dtype=np.int64)
+        b, o = ids // self.block, ids % self.block
+        return (o // self.pb) * (self.world * self.pb) + b * self.pb + o % self.pb
+
+    def piece_store(self, p):
+        """the contiguous rows of piece p (all ranks)"""
+        return self._store[p * self.world * self.pb:(p + 1) * self.world * self.pb]
+
+    def local_piece(self, p):
+        """this rank's [pb, D] slot inside piece p"""
+        r0 = p * self.world * self.pb + self.rank * self.pb
+        return self._store[r0:r0 + self.pb]
+
+    def set_local(self, x_local, degrees_local=None, op="copy"):
+        """scatter this rank's [rows <= block, dim] features into its slots, optionally scaled per row
+        (op 'rsqrt': the GCN factor of the source rows, applied before they travel)"""
+        from .plan import scale_rows
+        rows = x_local.size(0)
+        for p in range(self.pieces):
+            a, b = p * self.pb, min((p + 1) * self.pb, rows)
+            if b <= a:
+                break
+            dst = self.local_piece(p)[:b - a, :self.dim]
+            if op == "copy":
+                dst.copy_(x_local[a:b])
+            else:
+                scale_rows(x_local[a:b], degrees_local[a:b], op, out=dst)
+
+    def rows(self, index):
+        """the rows with global ids `index` (a LongTensor on this device)"""
+        return self.full[self.perm(index)]
+
+    def all_gather_piece(self, p):
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.piece_store(p), self.local_piece(p), group=self.group)
+
+
+class PieceMajorPipeline:
+    """All-gather overlapped with aggregation over a piece-major feature matrix.
+
+    Piece p of every block travels in one all_gather_into_tensor on a high-priority side stream, and the
+    rank's plan, split by source piece exactly like a single-GPU pass is split into source tiles, adds
+    piece p's entries into `out` as soon as it has landed.  The compute side is therefore the single-GPU
+    tiled pass (an L2-sized piece at a time), the transfer side is P plain collectives, and the two
+    overlap piece by piece.  GCN passes travel pre-scaled: each rank multiplies its own rows by
+    rsqrt(degrees) on the way into its slots and the kernels run ROF_MODE_GCN_PRESCALED, because source
+    rows are addressed by buffer row while `degrees` stays indexed by node id.
+    """
+
+    @staticmethod
+    def default_pieces(num_nodes, dim, world, entries_per_row=None, piece_bytes=64e6, min_entries_per_piece=48):
+        """pieces of about `piece_bytes` of features (L2-sized), but no more than leave a destination
+        `min_entries_per_piece` gathered rows per piece: every piece is one more pass over the destination
+        rows, and short rows lose more to that than the overlap returns (2 B200s, community graph, 21
+        entries per row: 1.30 ms per step with one piece, 1.71 ms with two).  One piece = one all-gather,
+        then the whole plan."""
+        pieces = max(1, round(num_nodes * dim * 4 / piece_bytes))
+        if entries_per_row is not None:
+            pieces = min(pieces, max(1, int(entries_per_row // min_entries_per_piece)))
+        return int(min(8, max(1, pieces)))
+
+    @staticmethod
+    def plan_from_v2(features, uniqpart_column_index, uniqpart_pointers, part2Node_ptr, part2Node_col, device=None):
+        """the rank's ROF_v2 plan over the piece-major matrix: source ids mapped to buffer rows"""
+        from .plan import AggregationPlan
+        f = features
+        col = f.perm(np.asarray(uniqpart_column_index)).astype(np.int32)
+        i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32))
+        return AggregationPlan.from_v2(f.size, i32(col), i32(uniqpart_pointers), i32(part2Node_ptr), i32(part2Node_col),
+                                       rows=f.blocks[f.rank], device=device or f.device)
+
+    def __init__(self, plan, features: PieceMajorFeatures, like=None):
+        f = features
+        if (plan.info["row_begin"], plan.info["row_end"]) != tuple(f.blocks[f.rank]) or plan.info["num_nodes"] != f.size:
+            raise RuntimeError("the plan must cover this rank's row block over the piece-major matrix (plan_from_v2)")
+        self.plan, self.features = plan, f
+        self.stage_plans = like.stage_plans if like is not None else (
+            plan.stages(f.world * f.pb, list(range(f.pieces))) if f.pieces > 1 else [plan])
+        self.comm_stream = torch.cuda.Stream(f.device, priority=-1) if f.world > 1 else None
+        self.ready = torch.cuda.Event() if f.world > 1 else None
+        self.landed = [torch.cuda.Event() for _ in range(f.pieces)]
+        self.launches = 0
+        self._prepared = None
+
+    def pad_degrees(self, degrees):
+        """degrees ([num_nodes], indexed by node id) padded to the buffer's row count, as the plan expects"""
+        f = self.features
+        out = torch.ones(f.size, dtype=degrees.dtype, device=degrees.device)
+        out[:f.n] = degrees
+        return out
+
+    def _transfer(self, cur):
+        f = self.features
+        self.ready.record(cur)
+        with torch.cuda.stream(self.comm_stream):
+            self.comm_stream.wait_event(self.ready)
+            for p in range(f.pieces):
+                f.all_gather_piece(p)
+                self.landed[p].record(self.comm_stream)
+
+    def _compute(self, cur, degrees_padded, mode, out, wait=True):
+        f = self.features
+        kmode = "gcn_prescaled" if mode == "gcn" else mode
+        key = (out.data_ptr(), tuple(out.shape), out.stride(0),
+               degrees_padded.data_ptr() if degrees_padded is not None else 0, kmode)
+        fast = self._prepared[1] if (self._prepared is not None and self._prepared[0] == key) else None
+        launches, prepared = 0, []
+        for p, sp in enumerate(self.stage_plans):
+            if wait and f.world > 1:
+                cur.wait_event(self.landed[p])
+            if fast is not None:
+                fn, args = fast[p]
+                args[-1] = ctypes.c_void_p(cur.cuda_stream)
+                with torch.cuda.device(f.device):
+                    _native.check(fn(*args))
+            else:
+                sp.aggregate(f.full, degrees_padded, kmode, out=out, accumulate=p > 0)
+                launches += sp.last_launch_count()
+                prepared.append(sp.prepared_call(f.full, degrees_padded, kmode, out, p > 0))
+        if fast is None:
+            self.launches = launches
+            self._prepared = (key, prepared)
+        return out
+
+    def aggregate(self, x_local, degrees_padded, mode, out):
+        """x_local: this rank's [rows, dim] features (unscaled), or None when its slots are already filled;
+        degrees_padded: pad_degrees(degrees) (None for 'sum')"""
+        f = self.features
+        cur = torch.cuda.current_stream(f.device)
+        if x_local is not None:
+            r0, r1 = f.blocks[f.rank]
+            if mode == "gcn":
+                f.set_local(x_local, degrees_padded[r0:r1], "rsqrt")
+            else:
+                f.set_local(x_local)
+        if f.world > 1:
+            self._transfer(cur)
+        return self._compute(cur, degrees_padded, mode, out)
+
+    def transfer_only(self):
+        if self.features.world <= 1:
+            return
+        cur = torch.cuda.current_stream(self.features.device)
+        self._transfer(cur)
+        for ev in self.landed:
+            cur.wait_event(ev)
+
+    def aggregate_only(self, degrees_padded, mode, out):
+        return self._compute(torch.cuda.current_stream(self.features.device), degrees_padded, mode, out, wait=False)

@@ -296,8 +296,13 @@ def workload_config(args, g, ratios):
                      f"D={args.dim}, {args.mode} aggregation, forward+backward pass per step",
          "part_size": args.part_size, "layout": "ROF_v2", "scale": args.scale, "source_tiles": args.tiles,
          "l2": "feature matrix and index arrays together exceed L2 (126 MB); no flush between iterations",
-         "parallelism": (f"row-block x{args.gpus} (blocks of equal work), "
-                         + ("staged send/receive rounds overlapped with per-stage aggregation"
+         "parallelism": (f"row-block x{args.gpus}, "
+                         + ({"pieces": "piece-major features: one all-gather per L2-sized piece of every block, overlapped "
+                                       "with the aggregation of the piece before",
+                             "columns": "features exchanged in column chunks, one all-gather each, overlapped with the "
+                                        "chunks' aggregation",
+                             "stages": "blocks of equal work, staged send/receive overlapped with per-stage aggregation"
+                             }[getattr(args, "pipeline_kind", "pieces")]
                             if args.pipeline else "all-gather then aggregate"))
          if args.gpus > 1 else "single GPU"}
     if ratios is not None:
@@ -313,23 +318,33 @@ class Job:
         import torch
         from artifact_b200 import search
         from artifact_b200.plan import AggregationPlan
-        from artifact_b200.sharding import PipelinedAggregator, ShardedFeatures, row_blocks
+        from artifact_b200.sharding import (ColumnChunkedFeatures, ColumnPipelinedAggregator, PieceMajorFeatures,
+                                            PieceMajorPipeline, PipelinedAggregator, ShardedFeatures, row_blocks)
         self.torch, self.ns, self.rank, self.world, self.dev = torch, ns, rank, world, dev
         self.g, self.L, self.t_graph, self.t_search = prepare_workload(ns, rank, world)
         g, L = self.g, self.L
         self.n, self.E, self.D, self.mode = g.num_nodes, g.num_edges, ns.dim, ns.mode
         self.ratios = search.reuse_ratios(L)
         n, D = self.n, self.D
-        pipelined = world > 1 and ns.pipeline
-        # blocks of equal work for the staged pipeline (its transfers are point to point and take any
-        # block size); the one-collective path needs equal row counts
-        self.blk, self.blocks = row_blocks(n, world, indptr=g.indptr_dst if pipelined else None)
+        kind = getattr(ns, "pipeline_kind", "pieces") if (world > 1 and ns.pipeline) else None
+        self.kind = kind
+        # the staged pipeline's transfers are point to point and take any block size: blocks of equal work;
+        # the collectives of the other paths need equal row counts
+        self.blk, self.blocks = row_blocks(n, world, indptr=g.indptr_dst if kind == "stages" else None)
         self.r0, self.r1 = self.blocks[rank]
         t0 = time.time()
         i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32))
-        v2 = [i32(L[k]) for k in ("uniqpart_column_index", "uniqpart_pointers", "part2Node_ptr", "part2Node_col")]
-        self.plan = AggregationPlan.from_v2(n, *v2, rows=(self.r0, self.r1), device=dev)
-        del v2
+        self.full_x = self.full_g = None
+        if kind == "pieces":
+            P = getattr(ns, "pieces", 0) or PieceMajorPipeline.default_pieces(n, D, world, g.num_edges / max(n, 1))
+            self.feat_x = PieceMajorFeatures(n, D, rank, world, dev, P)
+            self.feat_g = PieceMajorFeatures(n, D, rank, world, dev, P)
+            self.plan = PieceMajorPipeline.plan_from_v2(self.feat_x, *[L[k] for k in (
+                "uniqpart_column_index", "uniqpart_pointers", "part2Node_ptr", "part2Node_col")], device=dev)
+        else:
+            v2 = [i32(L[k]) for k in ("uniqpart_column_index", "uniqpart_pointers", "part2Node_ptr", "part2Node_col")]
+            self.plan = AggregationPlan.from_v2(n, *v2, rows=(self.r0, self.r1), device=dev)
+            del v2
         # the plan uses the groups only where they save enough gathered rows (rof_plan_create_v2)
         self.ratios["groups_used_by_this_rank_s_plan"] = self.plan.info["num_groups"]
         self.ratios["gathered_rows_of_this_rank_s_plan"] = self.plan.info["gather_entries"]
@@ -339,25 +354,46 @@ class Job:
                                                     rows=(self.r0, self.r1), device=dev)
         self.deg = torch.from_numpy(np.maximum(g.degrees_f32(), 1.0)).to(dev)
         gen = torch.Generator(device=dev); gen.manual_seed(1234)
-        bounds = self.blocks if pipelined else None
-        self.feat_x = ShardedFeatures(n, D, rank, world, dev, bounds=bounds)
-        self.feat_g = ShardedFeatures(n, D, rank, world, dev, bounds=bounds)
-        # every rank draws the same full matrices, so the all-gathered content is what it already holds
-        self.feat_x.full.normal_(generator=gen); self.feat_g.full.normal_(generator=gen)
         rows = self.r1 - self.r0
         self.out_f = torch.empty((rows, D), device=dev)
         self.out_b = torch.empty((rows, D), device=dev)
-        if world == 1 or not ns.pipeline:
-            self.tiles = self.plan.auto_tiles(D) if ns.tiles == "auto" else int(ns.tiles)
-        else:
-            self.tiles = 1                 # the pipeline's stages are already source-blocked
         self.pipes = {}
-        if pipelined:
-            sched = [[int(k) for k in st.split(",")] for st in ns.schedule.split("|")] if ns.schedule else None
-            px = PipelinedAggregator(self.plan, self.feat_x, schedule=sched, pieces=getattr(ns, "pieces", 0) or None)
-            self.pipes = {id(self.feat_x): px, id(self.feat_g): PipelinedAggregator(self.plan, self.feat_g, like=px)}
-            self.stage_info = {"peer_groups": px.schedule, "pieces_per_group": px.pieces,
-                               "transfer_stages": len(px.transfers), "compute_stages": len(px.stage_plans)}
+        self.tiles = 1
+        if kind == "pieces":
+            # every rank draws the same full row-major matrices: its own rows are what it contributes per
+            # pass (scattered, and for GCN scaled, into its slots of the piece-major buffer), the rest is
+            # what the output check compares against
+            self.full_x = torch.empty((n, D), device=dev).normal_(generator=gen)
+            self.full_g = torch.empty((n, D), device=dev).normal_(generator=gen)
+            px = PieceMajorPipeline(self.plan, self.feat_x)
+            self.pipes = {id(self.feat_x): px, id(self.feat_g): PieceMajorPipeline(self.plan, self.feat_g, like=px)}
+            self.deg_pad = px.pad_degrees(self.deg)
+            self.stage_info = {"kind": "piece-major features, one all-gather per piece, plan split by piece",
+                               "pieces": self.feat_x.pieces, "rows_per_rank_and_piece": self.feat_x.pb}
+        elif kind == "columns":
+            # every rank draws the same full matrices, so the all-gathered content is what it already holds
+            self.feat_x = ColumnChunkedFeatures(n, D, rank, world, dev, chunks=getattr(ns, "chunks", 0) or None)
+            self.feat_g = ColumnChunkedFeatures(n, D, rank, world, dev, chunks=getattr(ns, "chunks", 0) or None)
+            self.feat_x.fill_normal_(gen); self.feat_g.fill_normal_(gen)
+            px = ColumnPipelinedAggregator(self.plan, self.feat_x)
+            self.pipes = {id(self.feat_x): px, id(self.feat_g): ColumnPipelinedAggregator(self.plan, self.feat_g)}
+            self.stage_info = {"kind": "column chunks, one all-gather each", "column_chunks": self.feat_x.cols,
+                               "source_tiles_per_chunk": px.tiles}
+        else:
+            bounds = self.blocks if kind == "stages" else None
+            self.feat_x = ShardedFeatures(n, D, rank, world, dev, bounds=bounds)
+            self.feat_g = ShardedFeatures(n, D, rank, world, dev, bounds=bounds)
+            self.feat_x.full.normal_(generator=gen); self.feat_g.full.normal_(generator=gen)
+            if kind == "stages":
+                sched = [[int(k) for k in st.split(",")] for st in ns.schedule.split("|")] if ns.schedule else None
+                px = PipelinedAggregator(self.plan, self.feat_x, schedule=sched, pieces=getattr(ns, "pieces", 0) or None)
+                self.pipes = {id(self.feat_x): px,
+                              id(self.feat_g): PipelinedAggregator(self.plan, self.feat_g, like=px)}
+                self.stage_info = {"kind": "stages of source blocks, grouped send/receive", "peer_groups": px.schedule,
+                                   "pieces_per_group": px.pieces, "transfer_stages": len(px.transfers),
+                                   "compute_stages": len(px.stage_plans)}
+            else:
+                self.tiles = self.plan.auto_tiles(D) if ns.tiles == "auto" else int(ns.tiles)
         self.t_plan = time.time() - t0
         self.launches = 0
         self.gather_events = []
@@ -366,12 +402,16 @@ class Job:
         return self.torch.cuda.Event(enable_timing=True)
 
     def one_pass(self, p, feat, out, timed_gather=False):
-        if self.pipes and p is self.plan:       # transfers overlapped with the per-stage aggregation
+        if self.pipes and p is self.plan:       # transfers overlapped with the aggregation
             pipe = self.pipes[id(feat)]
-            pipe.aggregate(None, self.deg, self.mode, out)
+            if self.kind == "pieces":
+                full = self.full_x if feat is self.feat_x else self.full_g
+                pipe.aggregate(full[self.r0:self.r1], self.deg_pad, self.mode, out)
+            else:
+                pipe.aggregate(None, self.deg, self.mode, out)
             self.launches += pipe.launches
             return
-        xs = feat.all_gather(None) if self.world > 1 else feat.full[:self.n]
+        xs = feat.all_gather(None) if self.world > 1 else feat.full[:self.n]           # one collective, then the plan
         p.aggregate(xs, self.deg, self.mode, out=out, tiles=self.tiles,
                     gather_events=self.gather_events if timed_gather else None)
         self.launches += p.last_launch_count()
@@ -429,11 +469,14 @@ class Job:
             pick |= set(rng.integers(0, r1 - r0, size=max(0, rows_wanted - len(pick))).tolist())
             deg64 = np.maximum(g.degrees_f32(), 1.0).astype(np.float64)
             for feat, out in ((self.feat_x, self.out_f), (self.feat_g, self.out_b)):
-                full = feat.full[:self.n]
+                if self.kind == "pieces":
+                    fetch = (lambda ix, full=(self.full_x if feat is self.feat_x else self.full_g): full[ix])
+                else:
+                    fetch = feat.rows if hasattr(feat, "rows") else (lambda ix, full=feat.full[:self.n]: full[ix])
                 for lr in sorted(pick):
                     v = r0 + lr
                     idx = g.indices_src[ip[v]:ip[v + 1]].astype(np.int64)
-                    xs = full[torch.from_numpy(idx).to(self.dev)].cpu().numpy().astype(np.float64)
+                    xs = fetch(torch.from_numpy(idx).to(self.dev)).cpu().numpy().astype(np.float64)
                     if self.mode == "gcn":
                         want = (xs / np.sqrt(deg64[idx])[:, None]).sum(0) / np.sqrt(deg64[v])
                     elif self.mode == "mean":
@@ -460,7 +503,26 @@ class Job:
     def roofline(self, hbm_peak, peak_kind):
         torch = self.torch
         ge = self.gather_events
-        if not ge:             # pipelined run: time this rank's whole-block gather on its own
+        chunks = 1
+        if not ge and self.kind == "columns":      # phase B of every column chunk, bracketed by events
+            f = self.feat_x
+            chunks = len(f.cols)
+            px = self.pipes[id(f)]
+            for i in range(8):
+                for k, (c0, c1) in enumerate(f.cols):
+                    self.plan.aggregate(f.chunk_full(k), self.deg, self.mode, out=self.out_f[:, c0:c1], tiles=px.tiles[k],
+                                        gather_events=ge if i >= 3 else None)
+            torch.cuda.synchronize()
+            per_pass = sum(px.tiles)
+        elif not ge and self.kind == "pieces":     # phase B of every piece's plan
+            px = self.pipes[id(self.feat_x)]
+            for i in range(8):
+                for k, sp in enumerate(px.stage_plans):
+                    sp.aggregate(self.feat_x.full, self.deg_pad, "gcn_prescaled" if self.mode == "gcn" else self.mode,
+                                 out=self.out_f, accumulate=k > 0, gather_events=ge if i >= 3 else None)
+            torch.cuda.synchronize()
+            per_pass = len(px.stage_plans)
+        elif not ge:           # staged run: time this rank's whole-block gather on its own
             xs = self.feat_x.full[:self.n]
             for i in range(8):
                 e0, e1 = self.ev(), self.ev()
@@ -468,12 +530,15 @@ class Job:
                 if i >= 3:
                     ge.append((e0, e1))
             torch.cuda.synchronize()
-        per_pass = max(self.tiles, 1) if not self.pipes else 1
+            per_pass = 1
+        else:
+            per_pass = max(self.tiles, 1)
         gms = float(np.sum([a.elapsed_time(b) for a, b in ge])) / (len(ge) / per_pass)
         info, rows, D = self.plan.info, self.r1 - self.r0, self.D
-        gather_bytes = 4.0 * D * (info["gather_entries"] + rows) + 4.0 * info["gather_entries"] + 4.0 * (rows + 1)
+        # a pass over K column chunks reads the index entries (and degrees) once per chunk
+        gather_bytes = 4.0 * D * (info["gather_entries"] + rows) + chunks * (4.0 * info["gather_entries"] + 4.0 * (rows + 1))
         if self.mode == "gcn":
-            gather_bytes += 4.0 * (info["gather_entries"] - info["partial_entries"])
+            gather_bytes += chunks * 4.0 * (info["gather_entries"] - info["partial_entries"])
         achieved = gather_bytes / (gms / 1e3) / 1e9
         kernel = "gather_tiles_kernel + gather_rows_kernel (phase B)" if info["num_tiles"] else "gather_rows_kernel (phase B)"
         r = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
@@ -491,35 +556,57 @@ class Job:
         if not self.pipes:
             return None
         px, pg = self.pipes[id(self.feat_x)], self.pipes[id(self.feat_g)]
-        t_all, _, _ = self._bracket(lambda: (px.aggregate(None, self.deg, self.mode, self.out_f),
-                                             pg.aggregate(None, self.deg, self.mode, self.out_b)), iters, 2)
+        deg = self.deg_pad if self.kind == "pieces" else self.deg
+        t_all, _, _ = self._bracket(lambda: (self.one_pass(self.plan, self.feat_x, self.out_f),
+                                             self.one_pass(self.plan, self.feat_g, self.out_b)), iters, 2)
         t_tr, _, _ = self._bracket(lambda: (px.transfer_only(), pg.transfer_only()), iters, 2)
-        t_ag, _, _ = self._bracket(lambda: (px.aggregate_only(self.deg, self.mode, self.out_f),
-                                            pg.aggregate_only(self.deg, self.mode, self.out_b)), iters, 2)
+        t_ag, _, _ = self._bracket(lambda: (px.aggregate_only(deg, self.mode, self.out_f),
+                                            pg.aggregate_only(deg, self.mode, self.out_b)), iters, 2)
         recv = sum((b - a) for i, (a, b) in enumerate(self.blocks) if i != self.rank) * self.D * 4
+        if self.kind == "columns":               # whole padded blocks travel
+            recv = (self.world - 1) * self.feat_x.block * sum(st.shape[1] for st in self.feat_x._stores) * 4
+        if self.kind == "pieces":
+            recv = (self.world - 1) * self.feat_x.pieces * self.feat_x.pb * self.feat_x._store.shape[1] * 4
         return {"overlapped_ms": round(t_all, 4), "transfer_only_ms": round(t_tr, 4), "aggregate_only_ms": round(t_ag, 4),
                 "received_bytes_per_pass": int(recv),
                 "receive_GBs_transfer_only": round(2 * recv / (t_tr / 1e3) / 1e9, 1) if t_tr > 0 else None,
-                "note": "per step (two passes), max over ranks: the staged send/receive schedule without kernels, the "
-                        "per-stage kernels without transfers, and both together"}
+                "note": "per step (two passes), max over ranks: the transfers of the pipeline without its kernels, its "
+                        "kernels without transfers, and both together"}
 
     # ---- end to end: pinned host buffers in and out, copies inside the timed region -----------
     def e2e(self, steps):
         torch = self.torch
         from artifact_b200.streaming import HostStreamedAggregator
         rows, D, n = self.r1 - self.r0, self.D, self.n
-        up_rows = self.feat_x.local_view().shape[0]
-        h_x = torch.empty((up_rows, D), pin_memory=True); h_x.copy_(self.feat_x.local_view())
-        h_g = torch.empty((up_rows, D), pin_memory=True); h_g.copy_(self.feat_g.local_view())
+        columns = self.kind in ("columns", "pieces")
+        # what a pass's upload lands in: this rank's rows of the feature buffer, or (column chunks) a
+        # row-major staging block that the pass scatters into the chunk buffers first
+        def landing(feat):
+            return torch.empty((rows, D), device=self.dev) if columns else feat.local_view()
+        land_x, land_g = landing(self.feat_x), landing(self.feat_g)
+        up_rows = land_x.shape[0]
+        h_x = torch.empty((up_rows, D), pin_memory=True)
+        h_g = torch.empty((up_rows, D), pin_memory=True)
+        if self.kind == "pieces":
+            h_x.copy_(self.full_x[self.r0:self.r1]); h_g.copy_(self.full_g[self.r0:self.r1])
+        elif columns:
+            h_x.copy_(torch.cat([self.feat_x.chunk_local(k)[:rows] for k in range(len(self.feat_x.cols))], 1))
+            h_g.copy_(torch.cat([self.feat_g.chunk_local(k)[:rows] for k in range(len(self.feat_g.cols))], 1))
+        else:
+            h_x.copy_(land_x); h_g.copy_(land_g)
         h_of = torch.empty((rows, D), pin_memory=True)
         h_ob = torch.empty((rows, D), pin_memory=True)
         # two device slots: slot 0 is the benchmark's x buffers, slot 1 its gradient buffers; the forward
         # pass of a step goes through one, the backward pass through the other, so that the upload of a
         # pass overlaps the kernels of the pass before it and the download those of the pass after it
-        slots = []
-        for feat, out in ((self.feat_x, self.out_f), (self.feat_g, self.out_b)):
-            slots.append((feat.local_view(), out,
-                          (lambda feat=feat, out=out: self.one_pass(self.plan, feat, out))))
+        def run_pass(feat, land, out):
+            if columns:
+                self.pipes[id(feat)].aggregate(land, self.deg_pad if self.kind == "pieces" else self.deg, self.mode, out)
+                self.launches += self.pipes[id(feat)].launches
+            else:
+                self.one_pass(self.plan, feat, out)
+        slots = [(land_x, self.out_f, lambda: run_pass(self.feat_x, land_x, self.out_f)),
+                 (land_g, self.out_b, lambda: run_pass(self.feat_g, land_g, self.out_b))]
         hs = HostStreamedAggregator(slots, self.dev)
 
         def e2e_step(aggregate=True):
@@ -540,7 +627,12 @@ class Job:
         ms_e2e = run(True)
         ms_copy = run(False)
         # restore the device-resident inputs the other measurements use
-        self.feat_x.local_view().copy_(h_x); self.feat_g.local_view().copy_(h_g)
+        if self.kind == "pieces":
+            pass                                   # every pass scatters its rows into the buffer anyway
+        elif columns:
+            self.feat_x.set_local(h_x.to(self.dev)); self.feat_g.set_local(h_g.to(self.dev))
+        else:
+            self.feat_x.local_view().copy_(h_x); self.feat_g.local_view().copy_(h_g)
         torch.cuda.synchronize()
         return {"value": 2.0 * self.E / (ms_e2e / 1e3), "unit": "edges/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": 2 * n * D * 4, "d2h_bytes_per_step": 2 * n * D * 4,
@@ -551,7 +643,7 @@ class Job:
                         "are summed over the ranks; the graph plan stays resident like upstream's inputInfo tensors"}
 
     def release(self):
-        for k in ("plan", "plain", "pipes", "feat_x", "feat_g", "out_f", "out_b", "deg", "L", "g"):
+        for k in ("plan", "plain", "pipes", "feat_x", "feat_g", "full_x", "full_g", "out_f", "out_b", "deg", "L", "g"):
             setattr(self, k, None)
         self.torch.cuda.empty_cache()
 
@@ -655,6 +747,10 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (tests / profiling only)")
     ap.add_argument("--no-pipeline", dest="pipeline", action="store_false",
                     help="N > 1: one all-gather, then the aggregation (no overlap)")
+    ap.add_argument("--pipeline-kind", default="pieces", choices=["pieces", "columns", "stages"],
+                    help="N > 1: exchange the features piece-major (one all-gather per L2-sized piece of every block), "
+                         "in column chunks (one all-gather each) or in stages of source blocks (grouped send/receive)")
+    ap.add_argument("--chunks", type=int, default=0, help="N > 1, column pipeline: number of column chunks (0: by width)")
     ap.add_argument("--schedule", default="", help="N > 1 pipeline stages as ring offsets, e.g. '0|1,2,3|4,5,6,7'")
     ap.add_argument("--pieces", type=int, default=0, help="N > 1: pieces each peer group's transfer is cut into (0: by size)")
     ap.add_argument("--tiles", default="auto", help="source tiles per pass on one GPU: auto or an integer")

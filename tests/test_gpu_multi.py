@@ -62,7 +62,26 @@ def _worker(rank, world, port, name, q):
         for _ in range(2):
             pipe3.aggregate(None, deg, mode, out3)
         torch.cuda.synchronize()
-        res[mode] = (a, out.cpu().numpy(), out2.cpu().numpy(), (b0, out3.cpu().numpy()))
+        # features exchanged as column chunks, one all-gather each
+        from artifact_b200.sharding import ColumnChunkedFeatures, ColumnPipelinedAggregator
+        cf = ColumnChunkedFeatures(n, dim, rank, world, dev, chunks=3)
+        out4 = torch.empty((r1 - r0, dim), device=dev)
+        cp = ColumnPipelinedAggregator(plan, cf)
+        for _ in range(2):
+            cp.aggregate(local[:r1 - r0], deg, mode, out4)
+        torch.cuda.synchronize()
+        # piece-major features: one all-gather per piece, the plan reads permuted source ids
+        from artifact_b200.sharding import PieceMajorFeatures, PieceMajorPipeline
+        pf = PieceMajorFeatures(n, dim, rank, world, dev, 3)
+        pplan = PieceMajorPipeline.plan_from_v2(pf, *layout_args(g["layouts"], "v2"))
+        pp = PieceMajorPipeline(pplan, pf)
+        out5 = torch.empty((r1 - r0, dim), device=dev)
+        dpad = pp.pad_degrees(deg)
+        for _ in range(3):
+            pp.aggregate(local[:r1 - r0], dpad, mode, out5)
+        torch.cuda.synchronize()
+        res[mode] = (a, out.cpu().numpy(), out2.cpu().numpy(), (b0, out3.cpu().numpy()), out4.cpu().numpy(),
+                     out5.cpu().numpy())
     gathered = [None] * world
     dist.all_gather_object(gathered, (r0, res))
     if rank == 0:
@@ -102,6 +121,10 @@ def test_sharded_and_pipelined_match_oracle(name):
         assert_close(piped, want, what=f"pipelined, {mode}")
         piped2 = np.concatenate([r[mode][2] for _, r in sorted(gathered, key=lambda t: t[0])])
         assert_close(piped2, want, what=f"pipelined, two half stages, {mode}")
+        piped5 = np.concatenate([r[mode][5] for _, r in sorted(gathered, key=lambda t: t[0])])
+        assert_close(piped5, want, what=f"piece-major pipeline, {mode}")
+        piped4 = np.concatenate([r[mode][4] for _, r in sorted(gathered, key=lambda t: t[0])])
+        assert_close(piped4, want, what=f"column chunks, {mode}")
         piped3 = np.concatenate([o for _, o in sorted((r[mode][3] for _, r in gathered), key=lambda t: t[0])])
         assert_close(piped3, want, what=f"pipelined, blocks of equal work, transfers in 3 pieces, tiled stages, {mode}")
 

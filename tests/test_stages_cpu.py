@@ -118,3 +118,41 @@ def test_stage_ranges_are_checked():
         whole.stages_by_ranges([0, 8, 6, 12], [0, 1, 0])  # not ascending
     with pytest.raises(ValueError):
         whole.stages_by_ranges([0, 12], [0, 1])
+
+
+@pytest.mark.parametrize("name", ["c5_n1024_ps2", "c2_n640_ps2"])
+@pytest.mark.parametrize("world,rank,pieces", [(2, 1, 2), (4, 0, 3), (8, 5, 4)])
+def test_piece_major_layout_and_its_plans(name, world, rank, pieces):
+    """piece-major feature layout (one all-gather per piece): the map from node ids to buffer rows is
+    one-to-one, each rank's piece is contiguous where the collective puts it, and the rank's plan over
+    the permuted matrix — whole, and split by piece — gives the same sums as the plan over the
+    row-major matrix"""
+    import torch
+    from artifact_b200.sharding import PieceMajorFeatures, PieceMajorPipeline
+    g = load_golden(name)
+    n, L = g["N"], g["layouts"]
+    f = PieceMajorFeatures(n, 5, rank, world, torch.device("cpu"), pieces)
+    q = f.perm(np.arange(n))
+    assert len(np.unique(q)) == n and q.max() < f.size
+    for b, (a, e) in enumerate(f.blocks):
+        for p in range(pieces):
+            lo, hi = a + p * f.pb, min(a + (p + 1) * f.pb, e)
+            if hi > lo:
+                assert (q[lo:hi] == p * world * f.pb + b * f.pb + np.arange(hi - lo)).all()
+    r0, r1 = f.blocks[rank]
+    plain = AggregationPlan.from_v2(n, *layout_args(L, "v2"), rows=(r0, r1))
+    perm_plan = PieceMajorPipeline.plan_from_v2(f, *layout_args(L, "v2"))
+    assert perm_plan.info["num_nodes"] == f.size and perm_plan.info["original_edges"] == plain.info["original_edges"]
+    x = np.random.default_rng(1).standard_normal((n, 5)).astype(np.float32)
+    xp = np.zeros((f.size, 5), np.float32)
+    xp[q] = x
+    want = eval_plan_numpy(plain.export(), x, n)
+    assert np.allclose(eval_plan_numpy(perm_plan.export(), xp, f.size), want, rtol=1e-9, atol=1e-9)
+    got = np.zeros_like(want)
+    stages = perm_plan.stages(world * f.pb, list(range(pieces)))
+    for p, sp in enumerate(stages):
+        ex = sp.export()
+        src = ex["col"][ex["col"] < f.size]
+        assert ((src // (world * f.pb)) == p).all()          # stage p reads piece p only
+        got += eval_plan_numpy(ex, xp, f.size)
+    assert np.allclose(got, want, rtol=1e-9, atol=1e-9)
