@@ -302,7 +302,8 @@ def workload_config(args, g, ratios):
                              "columns": "features exchanged in column chunks, one all-gather each, overlapped with the "
                                         "chunks' aggregation",
                              "stages": "blocks of equal work, staged send/receive overlapped with per-stage aggregation"
-                             }[getattr(args, "pipeline_kind", "pieces")]
+                             }[("stages" if args.gpus <= 2 else "pieces") if getattr(args, "pipeline_kind", "auto") == "auto"
+                               else args.pipeline_kind]
                             if args.pipeline else "all-gather then aggregate"))
          if args.gpus > 1 else "single GPU"}
     if ratios is not None:
@@ -326,7 +327,11 @@ class Job:
         self.n, self.E, self.D, self.mode = g.num_nodes, g.num_edges, ns.dim, ns.mode
         self.ratios = search.reuse_ratios(L)
         n, D = self.n, self.D
-        kind = getattr(ns, "pipeline_kind", "pieces") if (world > 1 and ns.pipeline) else None
+        kind = getattr(ns, "pipeline_kind", "auto") if (world > 1 and ns.pipeline) else None
+        if kind == "auto":
+            # two ranks: the own block is half of the matrix and needs no transfer (stages); more ranks: the own
+            # block is small and the stages' point-to-point transfers fall behind the collectives (pieces)
+            kind = "stages" if world <= 2 else "pieces"
         self.kind = kind
         # the staged pipeline's transfers are point to point and take any block size: blocks of equal work;
         # the collectives of the other paths need equal row counts
@@ -747,7 +752,7 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (tests / profiling only)")
     ap.add_argument("--no-pipeline", dest="pipeline", action="store_false",
                     help="N > 1: one all-gather, then the aggregation (no overlap)")
-    ap.add_argument("--pipeline-kind", default="pieces", choices=["pieces", "columns", "stages"],
+    ap.add_argument("--pipeline-kind", default="auto", choices=["auto", "pieces", "columns", "stages"],
                     help="N > 1: exchange the features piece-major (one all-gather per L2-sized piece of every block), "
                          "in column chunks (one all-gather each) or in stages of source blocks (grouped send/receive)")
     ap.add_argument("--chunks", type=int, default=0, help="N > 1, column pipeline: number of column chunks (0: by width)")
