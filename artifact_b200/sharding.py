@@ -584,13 +584,33 @@ class PieceMajorPipeline:
         return AggregationPlan.from_v2(f.size, i32(col), i32(uniqpart_pointers), i32(part2Node_ptr), i32(part2Node_col),
                                        rows=f.blocks[f.rank], device=device or f.device)
 
-    def __init__(self, plan, features: PieceMajorFeatures, like=None):
+    @staticmethod
+    def own_first_ranges(pieces, world, pb, rank):
+        """(range_bounds, stage_of_range) of the own-first split: the rank's own slot of every piece is
+        stage 0 (readable before any transfer), the rest of piece p is stage p + 1"""
+        bounds, stage = [0], []
+        for p in range(pieces):
+            base = p * world * pb
+            for end, st in ((base + rank * pb, p + 1), (base + (rank + 1) * pb, 0), (base + world * pb, p + 1)):
+                bounds.append(end)
+                stage.append(st)
+        return bounds, stage
+
+    def __init__(self, plan, features: PieceMajorFeatures, like=None, own_first=False):
+        """own_first: one more stage in front, over the rank's own rows, which need no transfer: it runs
+        while the first piece travels (otherwise nothing covers that all-gather) at the price of one more
+        pass over the destination rows."""
         f = features
         if (plan.info["row_begin"], plan.info["row_end"]) != tuple(f.blocks[f.rank]) or plan.info["num_nodes"] != f.size:
             raise RuntimeError("the plan must cover this rank's row block over the piece-major matrix (plan_from_v2)")
         self.plan, self.features = plan, f
-        self.stage_plans = like.stage_plans if like is not None else (
-            plan.stages(f.world * f.pb, list(range(f.pieces))) if f.pieces > 1 else [plan])
+        self.own_first = bool(like.own_first if like is not None else (own_first and f.world > 1))
+        if like is not None:
+            self.stage_plans = like.stage_plans
+        elif self.own_first:
+            self.stage_plans = plan.stages_by_ranges(*self.own_first_ranges(f.pieces, f.world, f.pb, f.rank))
+        else:
+            self.stage_plans = plan.stages(f.world * f.pb, list(range(f.pieces))) if f.pieces > 1 else [plan]
         self.comm_stream = torch.cuda.Stream(f.device, priority=-1) if f.world > 1 else None
         self.ready = torch.cuda.Event() if f.world > 1 else None
         self.landed = [torch.cuda.Event() for _ in range(f.pieces)]
@@ -620,9 +640,10 @@ class PieceMajorPipeline:
                degrees_padded.data_ptr() if degrees_padded is not None else 0, kmode)
         fast = self._prepared[1] if (self._prepared is not None and self._prepared[0] == key) else None
         launches, prepared = 0, []
+        first = 1 if self.own_first else 0           # stage s reads piece s - first (stage 0 of own-first: none)
         for p, sp in enumerate(self.stage_plans):
-            if wait and f.world > 1:
-                cur.wait_event(self.landed[p])
+            if wait and f.world > 1 and p >= first:
+                cur.wait_event(self.landed[p - first])
             if fast is not None:
                 fn, args = fast[p]
                 args[-1] = ctypes.c_void_p(cur.cuda_stream)

@@ -8,7 +8,64 @@ inputs and outputs are double-buffered on the device, uploads run on their own s
 on another, so the upload of pass k+1 and the download of pass k-1 overlap the kernels of pass k.
 A pass is then bounded by max(copy, aggregate) instead of their sum.
 """
+import contextlib
+import os
+
 import torch
+
+
+def _cpulist(text):
+    cpus = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        a, _, b = part.partition("-")
+        cpus.update(range(int(a), int(b or a) + 1))
+    return cpus
+
+
+def device_host_node(device_index, sysfs="/sys"):
+    """(numa node, cpus of that node) of the host socket the GPU's PCIe link hangs off, or (None, set())
+    where the platform does not say (one node, a VM that hides the topology, no sysfs)."""
+    try:
+        p = torch.cuda.get_device_properties(device_index)
+        bdf = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        node = int(open(f"{sysfs}/bus/pci/devices/{bdf}/numa_node").read())
+        if node < 0:
+            return None, set()
+        return node, _cpulist(open(f"{sysfs}/devices/system/node/node{node}/cpulist").read())
+    except Exception:
+        return None, set()
+
+
+@contextlib.contextmanager
+def near_device(device_index, sysfs="/sys"):
+    """Run the body on cores of the GPU's own host socket, so that pinned buffers allocated (and first
+    touched) inside it are local to the GPU's PCIe root: a copy between a GPU and memory of the other
+    socket crosses the inter-socket link, which all GPUs of a box then share.  Yields the node or None;
+    the thread's affinity is put back afterwards (compute threads started later see all cores again)."""
+    node, cpus = device_host_node(device_index, sysfs)
+    old = None
+    try:
+        if node is not None and hasattr(os, "sched_getaffinity"):
+            mine = os.sched_getaffinity(0)
+            if cpus & mine and (cpus & mine) != mine:
+                old = mine
+                os.sched_setaffinity(0, cpus & mine)
+            elif not (cpus & mine):
+                node = None
+        yield node
+    finally:
+        if old is not None:
+            os.sched_setaffinity(0, old)
+
+
+def pinned_near(device_index, shape, dtype=torch.float32):
+    """a pinned host tensor placed on the GPU's host socket where that can be told (near_device)"""
+    with near_device(device_index):
+        t = torch.empty(shape, dtype=dtype, pin_memory=True)
+        t.zero_()                      # first touch inside the binding
+    return t
 
 
 class _Slot:

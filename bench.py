@@ -291,6 +291,23 @@ def prepare_workload(args, rank, world):
     return result
 
 
+def pipeline_kind(args, world, g):
+    """--pipeline-kind auto: two ranks -> stages (the own block is half of the matrix and needs no transfer);
+    more ranks -> the stages' point-to-point transfers fall behind the collectives: piece-major where the rows
+    are long enough to be cut into pieces, else column chunks (8 B200s, 50 entries per row, D=256: 10.4 ms per
+    step in 4 column chunks, 10.9 ms with one all-gather and the whole plan, 11.9 ms in stages)."""
+    kind = getattr(args, "pipeline_kind", "auto")
+    if kind != "auto":
+        return kind
+    if world <= 2:
+        return "stages"
+    if getattr(args, "pieces", 0):
+        return "pieces"
+    from artifact_b200.sharding import PieceMajorPipeline
+    P = PieceMajorPipeline.default_pieces(g.num_nodes, args.dim, world, g.num_edges / max(g.num_nodes, 1))
+    return "pieces" if P > 1 else "columns"
+
+
 def workload_config(args, g, ratios):
     c = {"workload": f"{args.workload}: seeded synthetic graph N={g.num_nodes} E={g.num_edges}, fp32 features "
                      f"D={args.dim}, {args.mode} aggregation, forward+backward pass per step",
@@ -302,8 +319,7 @@ def workload_config(args, g, ratios):
                              "columns": "features exchanged in column chunks, one all-gather each, overlapped with the "
                                         "chunks' aggregation",
                              "stages": "blocks of equal work, staged send/receive overlapped with per-stage aggregation"
-                             }[("stages" if args.gpus <= 2 else "pieces") if getattr(args, "pipeline_kind", "auto") == "auto"
-                               else args.pipeline_kind]
+                             }[pipeline_kind(args, args.gpus, g)]
                             if args.pipeline else "all-gather then aggregate"))
          if args.gpus > 1 else "single GPU"}
     if ratios is not None:
@@ -327,11 +343,7 @@ class Job:
         self.n, self.E, self.D, self.mode = g.num_nodes, g.num_edges, ns.dim, ns.mode
         self.ratios = search.reuse_ratios(L)
         n, D = self.n, self.D
-        kind = getattr(ns, "pipeline_kind", "auto") if (world > 1 and ns.pipeline) else None
-        if kind == "auto":
-            # two ranks: the own block is half of the matrix and needs no transfer (stages); more ranks: the own
-            # block is small and the stages' point-to-point transfers fall behind the collectives (pieces)
-            kind = "stages" if world <= 2 else "pieces"
+        kind = pipeline_kind(ns, world, g) if (world > 1 and ns.pipeline) else None
         self.kind = kind
         # the staged pipeline's transfers are point to point and take any block size: blocks of equal work;
         # the collectives of the other paths need equal row counts
@@ -370,11 +382,12 @@ class Job:
             # what the output check compares against
             self.full_x = torch.empty((n, D), device=dev).normal_(generator=gen)
             self.full_g = torch.empty((n, D), device=dev).normal_(generator=gen)
-            px = PieceMajorPipeline(self.plan, self.feat_x)
+            px = PieceMajorPipeline(self.plan, self.feat_x, own_first=bool(getattr(ns, "own_first", 0)))
             self.pipes = {id(self.feat_x): px, id(self.feat_g): PieceMajorPipeline(self.plan, self.feat_g, like=px)}
             self.deg_pad = px.pad_degrees(self.deg)
             self.stage_info = {"kind": "piece-major features, one all-gather per piece, plan split by piece",
-                               "pieces": self.feat_x.pieces, "rows_per_rank_and_piece": self.feat_x.pb}
+                               "pieces": self.feat_x.pieces, "rows_per_rank_and_piece": self.feat_x.pb,
+                               "own_rows_first": px.own_first, "compute_stages": len(px.stage_plans)}
         elif kind == "columns":
             # every rank draws the same full matrices, so the all-gathered content is what it already holds
             self.feat_x = ColumnChunkedFeatures(n, D, rank, world, dev, chunks=getattr(ns, "chunks", 0) or None)
@@ -581,7 +594,7 @@ class Job:
     # ---- end to end: pinned host buffers in and out, copies inside the timed region -----------
     def e2e(self, steps):
         torch = self.torch
-        from artifact_b200.streaming import HostStreamedAggregator
+        from artifact_b200.streaming import HostStreamedAggregator, device_host_node, pinned_near
         rows, D, n = self.r1 - self.r0, self.D, self.n
         columns = self.kind in ("columns", "pieces")
         # what a pass's upload lands in: this rank's rows of the feature buffer, or (column chunks) a
@@ -590,8 +603,9 @@ class Job:
             return torch.empty((rows, D), device=self.dev) if columns else feat.local_view()
         land_x, land_g = landing(self.feat_x), landing(self.feat_g)
         up_rows = land_x.shape[0]
-        h_x = torch.empty((up_rows, D), pin_memory=True)
-        h_g = torch.empty((up_rows, D), pin_memory=True)
+        di = self.dev.index if self.dev.index is not None else torch.cuda.current_device()
+        h_x = pinned_near(di, (up_rows, D))
+        h_g = pinned_near(di, (up_rows, D))
         if self.kind == "pieces":
             h_x.copy_(self.full_x[self.r0:self.r1]); h_g.copy_(self.full_g[self.r0:self.r1])
         elif columns:
@@ -599,8 +613,8 @@ class Job:
             h_g.copy_(torch.cat([self.feat_g.chunk_local(k)[:rows] for k in range(len(self.feat_g.cols))], 1))
         else:
             h_x.copy_(land_x); h_g.copy_(land_g)
-        h_of = torch.empty((rows, D), pin_memory=True)
-        h_ob = torch.empty((rows, D), pin_memory=True)
+        h_of = pinned_near(di, (rows, D))
+        h_ob = pinned_near(di, (rows, D))
         # two device slots: slot 0 is the benchmark's x buffers, slot 1 its gradient buffers; the forward
         # pass of a step goes through one, the backward pass through the other, so that the upload of a
         # pass overlaps the kernels of the pass before it and the download those of the pass after it
@@ -641,10 +655,10 @@ class Job:
         torch.cuda.synchronize()
         return {"value": 2.0 * self.E / (ms_e2e / 1e3), "unit": "edges/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": 2 * n * D * 4, "d2h_bytes_per_step": 2 * n * D * 4,
-                "copy_only_ms": ms_copy,
+                "copy_only_ms": ms_copy, "host_numa_node": device_host_node(di)[0],
                 "note": "features and gradients copied from pinned host memory, both results copied back, every step "
                         "(artifact_b200.streaming.HostStreamedAggregator: uploads and downloads on their own streams, "
-                        "double-buffered on the device); copy_only_ms is the same schedule without the kernels; bytes "
+                        "double-buffered on the device, host buffers on the GPU's own socket where sysfs tells it); copy_only_ms is the same schedule without the kernels; bytes "
                         "are summed over the ranks; the graph plan stays resident like upstream's inputInfo tensors"}
 
     def release(self):
@@ -755,6 +769,8 @@ def main():
     ap.add_argument("--pipeline-kind", default="auto", choices=["auto", "pieces", "columns", "stages"],
                     help="N > 1: exchange the features piece-major (one all-gather per L2-sized piece of every block), "
                          "in column chunks (one all-gather each) or in stages of source blocks (grouped send/receive)")
+    ap.add_argument("--own-first", type=int, default=0, choices=[0, 1],
+                    help="N > 1, piece-major pipeline: a first stage over the rank's own rows while piece 0 travels")
     ap.add_argument("--chunks", type=int, default=0, help="N > 1, column pipeline: number of column chunks (0: by width)")
     ap.add_argument("--schedule", default="", help="N > 1 pipeline stages as ring offsets, e.g. '0|1,2,3|4,5,6,7'")
     ap.add_argument("--pieces", type=int, default=0, help="N > 1: pieces each peer group's transfer is cut into (0: by size)")

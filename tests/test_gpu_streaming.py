@@ -133,3 +133,39 @@ def test_piece_major_pipeline_on_one_gpu(dim, pieces):
     idx = torch.tensor([0, 1, n // 2, n - 1], device=DEV)
     got_rows = feats.rows(idx).cpu().numpy()                 # last pass was GCN: the buffer holds scaled rows
     assert_close(got_rows, x[idx.cpu().numpy()] / np.sqrt(deg_np[idx.cpu().numpy()])[:, None], what="scaled rows in the buffer")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world,rank,pieces", [(3, 1, 2), (4, 0, 1), (2, 1, 3)])
+def test_piece_major_own_rows_first(world, rank, pieces):
+    """rank `rank` of `world` emulated on one GPU (the whole piece-major buffer is filled here, nothing
+    travels): with own_first the plan has one stage more, over the rank's own slots, and the stages
+    together still give the block's rows of the operator"""
+    from artifact_b200.sharding import PieceMajorFeatures, PieceMajorPipeline
+    g = load_golden("c2_n640_ps2")
+    n, L, dim = g["N"], g["layouts"], 40
+    feats = PieceMajorFeatures(n, dim, rank, world, DEV, pieces)
+    plan = PieceMajorPipeline.plan_from_v2(feats, *layout_args(L, "v2"))
+    pipe = PieceMajorPipeline(plan, feats, own_first=True)
+    twin = PieceMajorPipeline(plan, feats, like=pipe)
+    assert pipe.own_first and twin.own_first and len(pipe.stage_plans) == pieces + 1
+    bounds, stage = PieceMajorPipeline.own_first_ranges(pieces, world, feats.pb, rank)
+    assert bounds[0] == 0 and bounds[-1] == feats.size and sorted(set(stage)) == list(range(pieces + 1))
+    own = sum(b - a for a, b, s in zip(bounds, bounds[1:], stage) if s == 0)
+    assert own == pieces * feats.pb
+    r0, r1 = feats.blocks[rank]
+    deg_np = np.maximum(g["degrees"], 1.0)
+    deg_pad = pipe.pad_degrees(torch.from_numpy(deg_np).to(DEV))
+    out = torch.empty((r1 - r0, dim), device=DEV)
+    rng = np.random.default_rng(world * 10 + rank)
+    where = feats.perm(torch.arange(n, device=DEV))
+    for mode in ("sum", "gcn", "mean"):
+        x = rng.standard_normal((n, dim)).astype(np.float32)
+        travelled = x / np.sqrt(deg_np)[:, None] if mode == "gcn" else x        # GCN rows travel pre-scaled
+        feats.full[where] = torch.from_numpy(travelled.astype(np.float32)).to(DEV)
+        for p in (pipe, twin, pipe):                                            # third time: prepared calls
+            out.fill_(float("nan"))
+            p.aggregate_only(deg_pad, mode, out)
+            want = rof_oracle.aggregate_v2(x, L["uniqpart_column_index"], deg_np, L["uniqpart_pointers"],
+                                           L["part2Node_ptr"], L["part2Node_col"], mode, True)[r0:r1]
+            assert_close(out.cpu().numpy(), want, what=f"own rows first, rank {rank}/{world}, {pieces} pieces, {mode}")

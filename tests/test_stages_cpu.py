@@ -156,3 +156,18 @@ def test_piece_major_layout_and_its_plans(name, world, rank, pieces):
         assert ((src // (world * f.pb)) == p).all()          # stage p reads piece p only
         got += eval_plan_numpy(ex, xp, f.size)
     assert np.allclose(got, want, rtol=1e-9, atol=1e-9)
+    # own rows first: stage 0 reads only the rank's own slots, stage p + 1 the rest of piece p
+    bounds, stage_of = PieceMajorPipeline.own_first_ranges(pieces, world, f.pb, rank)
+    own_rows = set(f.perm(np.arange(r0, r1)).tolist())
+    got = np.zeros_like(want)
+    own_stages = perm_plan.stages_by_ranges(bounds, stage_of)
+    assert len(own_stages) == pieces + 1
+    for s, sp in enumerate(own_stages):
+        ex = sp.export()
+        src = ex["col"][ex["col"] < f.size]
+        if s == 0:
+            assert set(src.tolist()) <= own_rows
+        else:
+            assert ((src // (world * f.pb)) == s - 1).all() and not (set(src.tolist()) & own_rows)
+        got += eval_plan_numpy(ex, xp, f.size)
+    assert np.allclose(got, want, rtol=1e-9, atol=1e-9)
