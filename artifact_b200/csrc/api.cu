@@ -149,6 +149,7 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
     a.mirror_ids = p->d_group_orig;
     a.num_nodes = p->num_nodes; a.row_begin = 0; a.dim = dim; a.weight_gcn = gcn; a.scale_mode = 0;
     a.out_padded = 1; a.kernel = kDefaultGatherKernel; a.status = p->d_status;
+    a.entries_per_item = (int)std::min<int64_t>(p->group_sources / std::max(1, p->num_groups), 1 << 20);
     e = launch_gather(a, stream, &g_last_launches);
     if (e != cudaSuccess) return cuda_fail(e, "phase A (group partial sums)");
   }
@@ -162,6 +163,7 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
     a.accumulate = accumulate;
     a.ep = ep;
     a.kernel = kDefaultGatherKernel; a.status = p->d_status;
+    a.entries_per_item = (int)std::min<int64_t>(p->gather_entries / std::max(1, num_items), 1 << 20);
     // short rows that share entries: staged once per tile in shared memory; the other items
     // (long rows, segments of split rows) follow with the lane-group kernel
     const bool tiled = p->tiled.num_tiles > 0 && tiles_supported(a);
@@ -172,6 +174,7 @@ int rof_aggregate_fused(const rof_plan* p, int phases, int mode, const float* x,
       a.items = fine ? p->tiled.d_rest_items_fine : p->tiled.d_rest_items;
       a.num_items = fine ? p->tiled.num_rest_fine : p->tiled.num_rest;
       a.kernel = kDefaultGatherKernel;
+      a.entries_per_item = 0;   // what the tiles left: long rows and segments
     }
     // when the caller wants the whole pass, the last segment of a split row to arrive finishes it
     if (num_split > 0 && (phases & ROF_PHASE_REDUCE) && fuse_reduce_enabled()) {

@@ -772,11 +772,31 @@ cudaError_t launch_one(const GatherArgs& a, cudaStream_t stream) {
   return cudaGetLastError();
 }
 
+// Rows of 17..32 vectors run on 16 lanes with two vectors per lane instead of a whole warp with
+// one: two items per warp halve what every item pays once (descriptor, column entries, shuffles,
+// the store) for the same bytes per load — measured on B200 at widths 100 and 128: 5-9 % faster on
+// rows of ~490 entries, 5-11 % at ~50, 18-22 % at 14-21.  Rows of 9..16 vectors gain from the same
+// step (8 lanes, two vectors) only when the items are very short (the reuse groups of phase A,
+// part_size entries each: 4 % of a pass); at 14 or 50 entries per row it loses 10-15 %.
+// ROF_SHORT_ROWS = 0 | 1 forces the old / the new shapes everywhere (experiments, tests).
+constexpr int kShortItemEntries = 6;
+
+static int lane_shape_override() {
+  const char* e = std::getenv("ROF_SHORT_ROWS");
+  return e == nullptr ? -1 : (e[0] == '1' ? 1 : 0);
+}
+
 template <int VEC>
 cudaError_t dispatch_width(const GatherArgs& a, cudaStream_t stream) {
   const int nvec = (a.dim + VEC - 1) / VEC;
   if (nvec <= 4) return launch_one<VEC, 4, 1, 4>(a, stream);
   if (nvec <= 8) return launch_one<VEC, 8, 1, 8>(a, stream);
+  if constexpr (VEC == 4) {
+    const int force = lane_shape_override();
+    if (nvec > 16 && nvec <= 32 && force != 0) return launch_one<VEC, 16, 2, 4>(a, stream);
+    if (nvec <= 16 && (force == 1 || (force < 0 && a.entries_per_item > 0 && a.entries_per_item <= kShortItemEntries)))
+      return launch_one<VEC, 8, 2, 4>(a, stream);
+  }
   if (nvec <= 16) return launch_one<VEC, 16, 1, 8>(a, stream);
   const int c = (nvec + 31) / 32;
   // wide rows (measured on B200, 114.6M-edge graph): 3 vectors per lane run best with two rows in
@@ -982,11 +1002,12 @@ cudaError_t launch_gather_tiles(const GatherArgs& a0, const TileArgs& t, cudaStr
   GatherArgs a = a0;
   a.out_vec = out_allows(a, 4) ? 1 : 0;
   const int nvec = (a.dim + 3) / 4;
+  const bool narrow = lane_shape_override() != 0;   // measured on the community graph: 11-18 % faster at every width from 36 to 128
   cudaError_t e;
   if (nvec <= 4) e = launch_tiles_one<4, 1, 4>(a, t, stream);
   else if (nvec <= 8) e = launch_tiles_one<8, 1, 8>(a, t, stream);
-  else if (nvec <= 16) e = launch_tiles_one<16, 1, 8>(a, t, stream);
-  else if (nvec <= 32) e = launch_tiles_one<32, 1, 8>(a, t, stream);
+  else if (nvec <= 16) e = narrow ? launch_tiles_one<8, 2, 4>(a, t, stream) : launch_tiles_one<16, 1, 8>(a, t, stream);
+  else if (nvec <= 32) e = narrow ? launch_tiles_one<16, 2, 4>(a, t, stream) : launch_tiles_one<32, 1, 8>(a, t, stream);
   else e = launch_tiles_one<32, 2, 4>(a, t, stream);
   if (e == cudaSuccess && launches) ++*launches;
   return e;

@@ -178,6 +178,7 @@ struct GatherArgs {
   int out_vec;      // set by launch_gather: `out` rows allow stores as wide as the loads
   int out_padded;   // `out` is library scratch with a padded leading dimension: a ragged last vector is stored whole
   int kernel;       // host policy: 0 lane groups, 1 shared-memory ring (used when the buffers allow it)
+  int entries_per_item;  // average entries of the launch's items (0: unknown); very short items get narrower lane groups
   // split rows finished by their last-arriving segment (all null: split_reduce_kernel does it)
   const int32_t* slot_owner;
   const SplitRow* split;

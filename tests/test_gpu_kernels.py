@@ -232,3 +232,28 @@ def test_v1_cache_mirror_with_source_tiles(name):
     assert_close(c3.cpu().numpy(), c1.cpu().numpy(), what="part_result_cache rows, tiled vs untiled")
     with pytest.raises(RuntimeError):
         plan.aggregate(xd, deg, "gcn", cache_result=torch.zeros((G + 1, dim + 1), device=DEV), tiles=3)
+
+
+@pytest.mark.parametrize("short", ["0", "1"])
+@pytest.mark.parametrize("name", ["c3_n1500_ps3", "c2_n640_ps2", "c5_n1024_ps2"])
+def test_short_item_lane_groups(monkeypatch, short, name):
+    """widths of 9..32 vectors run on half as many lanes per item (two vectors per lane) when the items
+    are short; forced on and off here over short and long rows, reuse groups (phase A items of
+    part_size entries) included, in every mode, with contiguous and padded outputs"""
+    monkeypatch.setenv("ROF_SHORT_ROWS", short)
+    monkeypatch.setenv("ROF_TILES", "0")
+    g = load_golden(name)
+    n, L = g["N"], g["layouts"]
+    deg_np = np.maximum(g["degrees"], 1.0)
+    deg = torch.from_numpy(deg_np).to(DEV)
+    plan = v2_plan(n, L)
+    for dim in (33, 36, 47, 64, 65, 100, 128):
+        x = np.random.default_rng(dim).standard_normal((n, dim)).astype(np.float32)
+        xp = padded(x)
+        for mode in ("sum", "gcn", "mean"):
+            want = oracle_v2(L, deg_np, x, mode)
+            got = plan.aggregate(xp, deg, mode)
+            assert_close(got.cpu().numpy(), want, what=f"short={short} {name} dim {dim} {mode}")
+        acc = torch.from_numpy(want.astype(np.float32)).to(DEV).contiguous()
+        plan.aggregate(xp, deg, "mean", out=acc, accumulate=True)
+        assert_close(acc.cpu().numpy(), 2 * want, what=f"short={short} {name} dim {dim} accumulate")
