@@ -174,10 +174,14 @@ def test_c1_class_width_7(kernel, which):
 
 @pytest.mark.parametrize("name", ["c5_n1024_ps2", "c5_n1024_ps4", "c3_n1500_ps3", "c1_full_ps2", "c2_n640_ps2"])
 @pytest.mark.parametrize("dim", [8, 47, 64, 100, 256])
-def test_shared_memory_tiles(name, dim, monkeypatch):
+@pytest.mark.parametrize("wide_groups", [False, True])
+def test_shared_memory_tiles(name, dim, wide_groups, monkeypatch):
     """the tile kernel (forced on): short rows read their shared entries from shared memory; all
-    three modes plus the pre-scaled one, padded rows, a staged pass and the fused epilogue"""
+    three modes plus the pre-scaled one, padded rows, a staged pass and the fused epilogue; with the
+    default lane groups (two vectors per lane up to 32 vectors) and with the one-vector shapes"""
     monkeypatch.setenv("ROF_TILES", "1")
+    if wide_groups:
+        monkeypatch.setenv("ROF_SHORT_ROWS", "0")
     monkeypatch.delenv("ROF_KERNEL", raising=False)
     g = load_golden(name)
     n, L = g["N"], g["layouts"]
