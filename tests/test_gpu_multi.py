@@ -80,8 +80,20 @@ def _worker(rank, world, port, name, q):
         for _ in range(3):
             pp.aggregate(local[:r1 - r0], dpad, mode, out5)
         torch.cuda.synchronize()
+        # destinations x sources grid: all-gather inside the column group, reduce-scatter of partial
+        # rows inside the destination group (2 GPUs: a 1 x 2 grid, reduce-scatter only; 4: 2 x 2)
+        from artifact_b200.grid import GridLayout, GridPipeline
+        gl = GridLayout(n, world, rank, GridPipeline.default_cols(world), chunks=3)
+        if mode == "sum":
+            grid_groups = GridPipeline.make_groups(gl)
+            grid_plans = gl.chunk_plans(g["indptr_dst"], g["indices_src"], device=dev)
+        gp = GridPipeline(gl, grid_plans, dim, dev, groups=grid_groups)
+        out6 = torch.empty((r1 - r0, dim), device=dev)
+        for _ in range(3):
+            gp.aggregate(local[:r1 - r0], deg[r0:r1], mode, out6)
+        torch.cuda.synchronize()
         res[mode] = (a, out.cpu().numpy(), out2.cpu().numpy(), (b0, out3.cpu().numpy()), out4.cpu().numpy(),
-                     out5.cpu().numpy())
+                     out5.cpu().numpy(), out6.cpu().numpy())
     gathered = [None] * world
     dist.all_gather_object(gathered, (r0, res))
     if rank == 0:
@@ -123,6 +135,8 @@ def test_sharded_and_pipelined_match_oracle(name):
         assert_close(piped2, want, what=f"pipelined, two half stages, {mode}")
         piped5 = np.concatenate([r[mode][5] for _, r in sorted(gathered, key=lambda t: t[0])])
         assert_close(piped5, want, what=f"piece-major pipeline, {mode}")
+        grid = np.concatenate([r[mode][6] for _, r in sorted(gathered, key=lambda t: t[0])])
+        assert_close(grid, want, what=f"destination x source grid, {mode}")
         piped4 = np.concatenate([r[mode][4] for _, r in sorted(gathered, key=lambda t: t[0])])
         assert_close(piped4, want, what=f"column chunks, {mode}")
         piped3 = np.concatenate([o for _, o in sorted((r[mode][3] for _, r in gathered), key=lambda t: t[0])])

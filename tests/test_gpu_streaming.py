@@ -169,3 +169,46 @@ def test_piece_major_own_rows_first(world, rank, pieces):
             want = rof_oracle.aggregate_v2(x, L["uniqpart_column_index"], deg_np, L["uniqpart_pointers"],
                                            L["part2Node_ptr"], L["part2Node_col"], mode, True)[r0:r1]
             assert_close(out.cpu().numpy(), want, what=f"own rows first, rank {rank}/{world}, {pieces} pieces, {mode}")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world,cols,chunks", [(4, 2, 3), (8, 4, 2), (2, 1, 2)])
+def test_grid_pipeline_ranks_emulated_on_one_gpu(world, cols, chunks):
+    """destination x source grid: every rank's buffers and chunk plans on one GPU, the all-gather
+    replaced by filling the source buffer, the reduce-scatter by adding the partial rows of a
+    destination group; kernels, scaling passes and the chunk-major row order are the real ones"""
+    from artifact_b200.grid import GridLayout, GridPipeline
+    from artifact_b200.plan import scale_rows
+    g = load_golden("c2_n640_ps2")
+    n, dim = g["N"], 20
+    deg_np = np.maximum(g["degrees"], 1.0)
+    deg = torch.from_numpy(deg_np).to(DEV)
+    L0 = g["layouts"]
+    rng = np.random.default_rng(world)
+    pipes = []
+    for rank in range(world):
+        gl = GridLayout(n, world, rank, cols, chunks)
+        pipes.append(GridPipeline(gl, gl.chunk_plans(g["indptr_dst"], g["indices_src"], device=DEV), dim, DEV))
+    for mode in ("sum", "gcn", "mean"):
+        x = rng.standard_normal((n, dim)).astype(np.float32)
+        xd = torch.from_numpy(x).to(DEV)
+        for p in pipes:                                            # own rows into the own slot (scaled for GCN)
+            r0, r1 = p.layout.blocks[p.layout.rank]
+            p.set_local(xd[r0:r1], deg[r0:r1], mode)
+        for p in pipes:                                            # "all-gather" inside the column group
+            for ii, rr in enumerate(p.layout.column_group()):
+                p._src[ii * p.layout.blk:(ii + 1) * p.layout.blk].copy_(pipes[rr].own_slot())
+        for p in pipes:
+            for q in range(chunks):
+                p.compute_chunk(q)
+        want = rof_oracle.aggregate_v2(x, L0["uniqpart_column_index"], deg_np, L0["uniqpart_pointers"],
+                                       L0["part2Node_ptr"], L0["part2Node_col"], mode, True)
+        for p in pipes:                                            # "reduce-scatter" inside the destination group
+            gl = p.layout
+            total = sum(pipes[rr]._partial for rr in gl.destination_group())
+            r0, r1 = gl.blocks[gl.rank]
+            mine = torch.cat([total[q * gl.c * gl.cb + gl.j * gl.cb:q * gl.c * gl.cb + (gl.j + 1) * gl.cb] for q in range(chunks)])
+            op = {"sum": "copy", "mean": "reciprocal", "gcn": "rsqrt"}[mode]
+            out = torch.empty((r1 - r0, dim), device=DEV)
+            scale_rows(mine[:r1 - r0, :dim], deg[r0:r1], op, out=out)
+            assert_close(out.cpu().numpy(), want[r0:r1], what=f"grid {world // cols}x{cols}, rank {gl.rank}, {mode}")
