@@ -96,6 +96,11 @@ CUDA_ABI = [
                                              c_void_p]),
     ("rof_scale_rows", c_int, [c_void_p, c_int64, c_int, c_void_p, c_int, c_void_p, c_int64, c_int64, c_void_p]),
     ("rof_probe_read", c_int, [c_void_p, c_int64, c_int, c_void_p, c_void_p]),
+    ("rof_copy_async", c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
+    ("rof_shared_alloc", c_int, [c_int64, ctypes.POINTER(c_void_p), c_void_p]),
+    ("rof_shared_open", c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    ("rof_shared_close", c_int, [c_void_p]),
+    ("rof_shared_free", c_int, [c_void_p]),
     ("rof_plan_take_status", c_int, [c_void_p]),
     ("rof_last_launch_count", c_int, []),
     ("rof_last_error", c_char_p, []),

@@ -1,6 +1,7 @@
 // The per-call entry points of the C ABI: argument checks, workspace carving, launches.
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 
 #include "rof_internal.h"
 
@@ -213,6 +214,56 @@ int rof_scale_rows(const float* x, int64_t ldx, int dim, const float* degrees, i
   const int pad_to = (int)std::min<int64_t>(round_up(dim, 4), ldo);
   const cudaError_t e = launch_scale_rows(x, ldx, degrees, out, ldo, (int)num_rows, dim, pad_to, op, (cudaStream_t)stream_);
   return e == cudaSuccess ? ROF_OK : cuda_fail(e, "rof_scale_rows");
+}
+
+int rof_copy_async(void* dst, const void* src, int64_t bytes, void* stream_) {
+  if (bytes < 0 || (bytes > 0 && (dst == nullptr || src == nullptr))) {
+    set_error("rof_copy_async: null pointer or negative size");
+    return ROF_ERR_BAD_ARGUMENT;
+  }
+  if (bytes == 0) return ROF_OK;
+  const cudaError_t e = cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, (cudaStream_t)stream_);
+  return e == cudaSuccess ? ROF_OK : cuda_fail(e, "rof_copy_async");
+}
+
+static_assert(sizeof(cudaIpcMemHandle_t) == ROF_SHARED_HANDLE_BYTES, "interprocess handle size");
+
+int rof_shared_alloc(int64_t bytes, void** ptr, unsigned char* handle) {
+  if (bytes <= 0 || ptr == nullptr || handle == nullptr) {
+    set_error("rof_shared_alloc: bad argument");
+    return ROF_ERR_BAD_ARGUMENT;
+  }
+  *ptr = nullptr;
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, (size_t)bytes);
+  if (e != cudaSuccess) { cudaGetLastError(); set_error("rof_shared_alloc: out of device memory"); return ROF_ERR_NO_MEMORY; }
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) { cudaFree(p); return cuda_fail(e, "cudaIpcGetMemHandle"); }
+  std::memcpy(handle, &h, sizeof(h));
+  *ptr = p;
+  return ROF_OK;
+}
+
+int rof_shared_open(const unsigned char* handle, void** ptr) {
+  if (handle == nullptr || ptr == nullptr) { set_error("rof_shared_open: null pointer"); return ROF_ERR_BAD_ARGUMENT; }
+  *ptr = nullptr;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, sizeof(h));
+  const cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? ROF_OK : cuda_fail(e, "cudaIpcOpenMemHandle");
+}
+
+int rof_shared_close(void* ptr) {
+  if (ptr == nullptr) return ROF_OK;
+  const cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? ROF_OK : cuda_fail(e, "cudaIpcCloseMemHandle");
+}
+
+int rof_shared_free(void* ptr) {
+  if (ptr == nullptr) return ROF_OK;
+  const cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? ROF_OK : cuda_fail(e, "cudaFree");
 }
 
 int rof_probe_read(const void* buffer, int64_t bytes, int repeats, float* sink, void* stream_) {

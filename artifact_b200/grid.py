@@ -189,12 +189,13 @@ class GridPipeline:
             self.reduced[q].record(self.comm)
 
     def aggregate(self, x_local, degrees_local, mode, out, transfers=True, kernels=True):
-        """x_local: this rank's [rows, dim] features; degrees_local: the degrees of the same rows
-        (None for 'sum'); out: [rows, dim].  transfers / kernels = False leave one side out (timing
-        breakdown: the buffers then hold whatever the last full pass left)."""
+        """x_local: this rank's [rows, dim] features (None: the own slot is already filled);
+        degrees_local: the degrees of the same rows (None for 'sum'); out: [rows, dim].
+        transfers / kernels = False leave one side out (timing breakdown: the buffers then hold
+        whatever the last full pass left)."""
         cur = torch.cuda.current_stream(self.device)
         launches = 0
-        if kernels:
+        if kernels and x_local is not None:
             self.set_local(x_local, degrees_local, mode)
             launches += 1
         if transfers:
@@ -214,3 +215,16 @@ class GridPipeline:
             launches += 1
         self.launches = launches
         return out
+
+    def transfer_only(self):
+        """the pass's collectives without its kernels (timing breakdown)"""
+        return self.aggregate(None, None, "sum", None, transfers=True, kernels=False)
+
+    def aggregate_only(self, degrees_local, mode, out):
+        """the pass's kernels over whatever the buffers hold, without collectives (timing breakdown)"""
+        return self.aggregate(None, degrees_local, mode, out, transfers=False, kernels=True)
+
+    def received_bytes_per_pass(self):
+        L = self.layout
+        ld = self._src.shape[1]
+        return ((L.r - 1) * L.blk + (L.c - 1) * L.q * L.cb) * ld * 4

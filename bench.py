@@ -318,7 +318,9 @@ def workload_config(args, g, ratios):
                                        "with the aggregation of the piece before",
                              "columns": "features exchanged in column chunks, one all-gather each, overlapped with the "
                                         "chunks' aggregation",
-                             "stages": "blocks of equal work, staged send/receive overlapped with per-stage aggregation"
+                             "stages": "blocks of equal work, staged send/receive overlapped with per-stage aggregation",
+                             "grid": "destination x source grid: all-gather inside the column group, partial rows "
+                                     "reduce-scattered inside the destination group chunk by chunk"
                              }[pipeline_kind(args, args.gpus, g)]
                             if args.pipeline else "all-gather then aggregate"))
          if args.gpus > 1 else "single GPU"}
@@ -352,7 +354,14 @@ class Job:
         t0 = time.time()
         i32 = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32))
         self.full_x = self.full_g = None
-        if kind == "pieces":
+        if kind == "grid":
+            from artifact_b200.grid import GridLayout, GridPipeline
+            self.grid = GridLayout(n, world, rank, getattr(ns, "grid_cols", 0) or GridPipeline.default_cols(world),
+                                   getattr(ns, "chunks", 0) or 4)
+            self.grid_groups = GridPipeline.make_groups(self.grid)
+            self.grid_plans = self.grid.chunk_plans(g.indptr_dst, g.indices_src, device=dev)
+            self.plan = self.grid_plans[0]
+        elif kind == "pieces":
             P = getattr(ns, "pieces", 0) or PieceMajorPipeline.default_pieces(n, D, world, g.num_edges / max(n, 1))
             self.feat_x = PieceMajorFeatures(n, D, rank, world, dev, P)
             self.feat_g = PieceMajorFeatures(n, D, rank, world, dev, P)
@@ -364,7 +373,8 @@ class Job:
             del v2
         # the plan uses the groups only where they save enough gathered rows (rof_plan_create_v2)
         self.ratios["groups_used_by_this_rank_s_plan"] = self.plan.info["num_groups"]
-        self.ratios["gathered_rows_of_this_rank_s_plan"] = self.plan.info["gather_entries"]
+        self.ratios["gathered_rows_of_this_rank_s_plan"] = (self.plan.info["gather_entries"] if kind != "grid" else
+                                                            sum(p.info["gather_entries"] for p in self.grid_plans))
         self.plain = None
         if want_plain:
             self.plain = AggregationPlan.from_parts(n, i32(g.indices_src), i32(g.indptr_dst), i32(np.arange(n)),
@@ -388,6 +398,17 @@ class Job:
             self.stage_info = {"kind": "piece-major features, one all-gather per piece, plan split by piece",
                                "pieces": self.feat_x.pieces, "rows_per_rank_and_piece": self.feat_x.pb,
                                "own_rows_first": px.own_first, "compute_stages": len(px.stage_plans)}
+        elif kind == "grid":
+            self.full_x = torch.empty((n, D), device=dev).normal_(generator=gen)
+            self.full_g = torch.empty((n, D), device=dev).normal_(generator=gen)
+            px = GridPipeline(self.grid, self.grid_plans, D, dev, groups=self.grid_groups)
+            pg = GridPipeline(self.grid, self.grid_plans, D, dev, like=px)
+            self.feat_x, self.feat_g = px, pg
+            self.pipes = {id(px): px, id(pg): pg}
+            self.deg_local = self.deg[self.r0:self.r1].contiguous()
+            self.stage_info = {"kind": "destination x source grid", "grid": [self.grid.r, self.grid.c],
+                               "destination_chunks": self.grid.q, "rows_per_rank_and_chunk": self.grid.cb,
+                               "received_rows_fraction": round((self.grid.r + self.grid.c - 2) / world, 4)}
         elif kind == "columns":
             # every rank draws the same full matrices, so the all-gathered content is what it already holds
             self.feat_x = ColumnChunkedFeatures(n, D, rank, world, dev, chunks=getattr(ns, "chunks", 0) or None)
@@ -399,15 +420,19 @@ class Job:
                                "source_tiles_per_chunk": px.tiles}
         else:
             bounds = self.blocks if kind == "stages" else None
-            self.feat_x = ShardedFeatures(n, D, rank, world, dev, bounds=bounds)
-            self.feat_g = ShardedFeatures(n, D, rank, world, dev, bounds=bounds)
+            transport = getattr(ns, "transport", "nccl") if kind == "stages" else "nccl"
+            self.feat_x = ShardedFeatures(n, D, rank, world, dev, bounds=bounds, shared=transport == "copy")
+            self.feat_g = ShardedFeatures(n, D, rank, world, dev, bounds=bounds, shared=transport == "copy")
             self.feat_x.full.normal_(generator=gen); self.feat_g.full.normal_(generator=gen)
             if kind == "stages":
                 sched = [[int(k) for k in st.split(",")] for st in ns.schedule.split("|")] if ns.schedule else None
-                px = PipelinedAggregator(self.plan, self.feat_x, schedule=sched, pieces=getattr(ns, "pieces", 0) or None)
+                px = PipelinedAggregator(self.plan, self.feat_x, schedule=sched, pieces=getattr(ns, "pieces", 0) or None,
+                                         transport=transport)
                 self.pipes = {id(self.feat_x): px,
-                              id(self.feat_g): PipelinedAggregator(self.plan, self.feat_g, like=px)}
-                self.stage_info = {"kind": "stages of source blocks, grouped send/receive", "peer_groups": px.schedule,
+                              id(self.feat_g): PipelinedAggregator(self.plan, self.feat_g, like=px, transport=transport)}
+                self.stage_info = {"kind": "stages of source blocks, " + ("grouped send/receive" if transport == "nccl" else
+                                                                         "peers' blocks pulled by the copy engines"),
+                                   "peer_groups": px.schedule,
                                    "pieces_per_group": px.pieces, "transfer_stages": len(px.transfers),
                                    "compute_stages": len(px.stage_plans)}
             else:
@@ -425,6 +450,9 @@ class Job:
             if self.kind == "pieces":
                 full = self.full_x if feat is self.feat_x else self.full_g
                 pipe.aggregate(full[self.r0:self.r1], self.deg_pad, self.mode, out)
+            elif self.kind == "grid":
+                full = self.full_x if feat is self.feat_x else self.full_g
+                pipe.aggregate(full[self.r0:self.r1], self.deg_local, self.mode, out)
             else:
                 pipe.aggregate(None, self.deg, self.mode, out)
             self.launches += pipe.launches
@@ -487,7 +515,7 @@ class Job:
             pick |= set(rng.integers(0, r1 - r0, size=max(0, rows_wanted - len(pick))).tolist())
             deg64 = np.maximum(g.degrees_f32(), 1.0).astype(np.float64)
             for feat, out in ((self.feat_x, self.out_f), (self.feat_g, self.out_b)):
-                if self.kind == "pieces":
+                if self.kind in ("pieces", "grid"):
                     fetch = (lambda ix, full=(self.full_x if feat is self.feat_x else self.full_g): full[ix])
                 else:
                     fetch = feat.rows if hasattr(feat, "rows") else (lambda ix, full=feat.full[:self.n]: full[ix])
@@ -540,6 +568,16 @@ class Job:
                                  out=self.out_f, accumulate=k > 0, gather_events=ge if i >= 3 else None)
             torch.cuda.synchronize()
             per_pass = len(px.stage_plans)
+        elif not ge and self.kind == "grid":       # the gather of every destination chunk
+            px = self.pipes[id(self.feat_x)]
+            for i in range(8):
+                for q in range(self.grid.q):
+                    e0, e1 = self.ev(), self.ev()
+                    e0.record(); px.compute_chunk(q); e1.record()
+                    if i >= 3:
+                        ge.append((e0, e1))
+            torch.cuda.synchronize()
+            per_pass = self.grid.q
         elif not ge:           # staged run: time this rank's whole-block gather on its own
             xs = self.feat_x.full[:self.n]
             for i in range(8):
@@ -553,6 +591,9 @@ class Job:
             per_pass = max(self.tiles, 1)
         gms = float(np.sum([a.elapsed_time(b) for a, b in ge])) / (len(ge) / per_pass)
         info, rows, D = self.plan.info, self.r1 - self.r0, self.D
+        if self.kind == "grid":                    # the rank's tile: partial rows of the whole destination group
+            info = dict(info, gather_entries=sum(p.info["gather_entries"] for p in self.grid_plans), partial_entries=0)
+            rows = self.grid.dst_rows
         # a pass over K column chunks reads the index entries (and degrees) once per chunk
         gather_bytes = 4.0 * D * (info["gather_entries"] + rows) + chunks * (4.0 * info["gather_entries"] + 4.0 * (rows + 1))
         if self.mode == "gcn":
@@ -574,7 +615,7 @@ class Job:
         if not self.pipes:
             return None
         px, pg = self.pipes[id(self.feat_x)], self.pipes[id(self.feat_g)]
-        deg = self.deg_pad if self.kind == "pieces" else self.deg
+        deg = self.deg_pad if self.kind == "pieces" else (self.deg_local if self.kind == "grid" else self.deg)
         t_all, _, _ = self._bracket(lambda: (self.one_pass(self.plan, self.feat_x, self.out_f),
                                              self.one_pass(self.plan, self.feat_g, self.out_b)), iters, 2)
         t_tr, _, _ = self._bracket(lambda: (px.transfer_only(), pg.transfer_only()), iters, 2)
@@ -585,6 +626,8 @@ class Job:
             recv = (self.world - 1) * self.feat_x.block * sum(st.shape[1] for st in self.feat_x._stores) * 4
         if self.kind == "pieces":
             recv = (self.world - 1) * self.feat_x.pieces * self.feat_x.pb * self.feat_x._store.shape[1] * 4
+        if self.kind == "grid":
+            recv = px.received_bytes_per_pass()
         return {"overlapped_ms": round(t_all, 4), "transfer_only_ms": round(t_tr, 4), "aggregate_only_ms": round(t_ag, 4),
                 "received_bytes_per_pass": int(recv),
                 "receive_GBs_transfer_only": round(2 * recv / (t_tr / 1e3) / 1e9, 1) if t_tr > 0 else None,
@@ -596,7 +639,7 @@ class Job:
         torch = self.torch
         from artifact_b200.streaming import HostStreamedAggregator, device_host_node, pinned_near
         rows, D, n = self.r1 - self.r0, self.D, self.n
-        columns = self.kind in ("columns", "pieces")
+        columns = self.kind in ("columns", "pieces", "grid")
         # what a pass's upload lands in: this rank's rows of the feature buffer, or (column chunks) a
         # row-major staging block that the pass scatters into the chunk buffers first
         def landing(feat):
@@ -606,7 +649,7 @@ class Job:
         di = self.dev.index if self.dev.index is not None else torch.cuda.current_device()
         h_x = pinned_near(di, (up_rows, D))
         h_g = pinned_near(di, (up_rows, D))
-        if self.kind == "pieces":
+        if self.kind in ("pieces", "grid"):
             h_x.copy_(self.full_x[self.r0:self.r1]); h_g.copy_(self.full_g[self.r0:self.r1])
         elif columns:
             h_x.copy_(torch.cat([self.feat_x.chunk_local(k)[:rows] for k in range(len(self.feat_x.cols))], 1))
@@ -620,7 +663,8 @@ class Job:
         # pass overlaps the kernels of the pass before it and the download those of the pass after it
         def run_pass(feat, land, out):
             if columns:
-                self.pipes[id(feat)].aggregate(land, self.deg_pad if self.kind == "pieces" else self.deg, self.mode, out)
+                deg = self.deg_pad if self.kind == "pieces" else (self.deg_local if self.kind == "grid" else self.deg)
+                self.pipes[id(feat)].aggregate(land, deg, self.mode, out)
                 self.launches += self.pipes[id(feat)].launches
             else:
                 self.one_pass(self.plan, feat, out)
@@ -646,7 +690,7 @@ class Job:
         ms_e2e = run(True)
         ms_copy = run(False)
         # restore the device-resident inputs the other measurements use
-        if self.kind == "pieces":
+        if self.kind in ("pieces", "grid"):
             pass                                   # every pass scatters its rows into the buffer anyway
         elif columns:
             self.feat_x.set_local(h_x.to(self.dev)); self.feat_g.set_local(h_g.to(self.dev))
@@ -662,7 +706,8 @@ class Job:
                         "are summed over the ranks; the graph plan stays resident like upstream's inputInfo tensors"}
 
     def release(self):
-        for k in ("plan", "plain", "pipes", "feat_x", "feat_g", "full_x", "full_g", "out_f", "out_b", "deg", "L", "g"):
+        for k in ("plan", "plain", "pipes", "feat_x", "feat_g", "full_x", "full_g", "out_f", "out_b", "deg", "L", "g",
+                  "grid_plans"):
             setattr(self, k, None)
         self.torch.cuda.empty_cache()
 
@@ -766,12 +811,15 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (tests / profiling only)")
     ap.add_argument("--no-pipeline", dest="pipeline", action="store_false",
                     help="N > 1: one all-gather, then the aggregation (no overlap)")
-    ap.add_argument("--pipeline-kind", default="auto", choices=["auto", "pieces", "columns", "stages"],
+    ap.add_argument("--transport", default="nccl", choices=["nccl", "copy"],
+                    help="N > 1, stage pipeline: grouped NCCL send/receive, or copy engines pulling from the peers' buffers")
+    ap.add_argument("--grid-cols", type=int, default=0, help="N > 1, grid pipeline: columns of the grid (0: by world size)")
+    ap.add_argument("--pipeline-kind", default="auto", choices=["auto", "pieces", "columns", "stages", "grid"],
                     help="N > 1: exchange the features piece-major (one all-gather per L2-sized piece of every block), "
                          "in column chunks (one all-gather each) or in stages of source blocks (grouped send/receive)")
     ap.add_argument("--own-first", type=int, default=0, choices=[0, 1],
                     help="N > 1, piece-major pipeline: a first stage over the rank's own rows while piece 0 travels")
-    ap.add_argument("--chunks", type=int, default=0, help="N > 1, column pipeline: number of column chunks (0: by width)")
+    ap.add_argument("--chunks", type=int, default=0, help="N > 1: column chunks of the column pipeline (0: by width), destination chunks of the grid (0: 4)")
     ap.add_argument("--schedule", default="", help="N > 1 pipeline stages as ring offsets, e.g. '0|1,2,3|4,5,6,7'")
     ap.add_argument("--pieces", type=int, default=0, help="N > 1: pieces each peer group's transfer is cut into (0: by size)")
     ap.add_argument("--tiles", default="auto", help="source tiles per pass on one GPU: auto or an integer")

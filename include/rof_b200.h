@@ -33,7 +33,7 @@ enum rof_status {
   ROF_ERR_BAD_LAYOUT = 2,     /* index tensors violate an invariant of the upstream layouts */
   ROF_ERR_CUDA = 3,           /* a CUDA runtime call failed; see rof_last_error() */
   ROF_ERR_WORKSPACE = 4,      /* workspace missing, misaligned or smaller than rof_plan_workspace_bytes() */
-  ROF_ERR_NO_MEMORY = 5,      /* host allocation failed while building a plan */
+  ROF_ERR_NO_MEMORY = 5,      /* host allocation failed while building a plan, or rof_shared_alloc found no device memory */
   ROF_ERR_WAIT_LIMIT = 6      /* a bounded device-side wait (shared-memory ring copies) gave up */
 };
 
@@ -272,6 +272,31 @@ int rof_scale_rows(const float* x, int64_t ldx, int dim, const float* degrees, i
  * `sink` is one device float the kernel may write.
  */
 int rof_probe_read(const void* buffer, int64_t bytes, int repeats, float* sink, void* stream);
+
+/*
+ * One asynchronous copy of `bytes` between two device buffers that this process can address: the
+ * current GPU's memory, or a peer GPU's mapped here (CUDA IPC, peer access).  No upstream
+ * counterpart (upstream runs on one GPU); it is the transport of the multi-GPU pipeline in which
+ * copy engines pull a peer's feature rows over NVLink while this GPU's SMs run the gather, which
+ * an SM-driven collective cannot do next to a kernel that saturates HBM.  Ordered on `stream`
+ * like any other call of this interface; no kernel is given the peer's memory.
+ */
+int rof_copy_async(void* dst, const void* src, int64_t bytes, void* stream);
+
+/*
+ * Device buffers that other processes of the box can map (one process per GPU): the feature
+ * buffer whose rows the peers pull with rof_copy_async.  rof_shared_alloc allocates `bytes` on the
+ * current GPU (its own allocation, so that the exported handle covers exactly this buffer) and
+ * writes the 64-byte interprocess handle; rof_shared_open maps another process' buffer into the
+ * current GPU's address space (peer access is enabled by the driver on first use) and
+ * rof_shared_close unmaps it; rof_shared_free releases an own buffer once no peer maps it any more.
+ * The handle travels between the processes by any host channel (here: torch.distributed objects).
+ */
+#define ROF_SHARED_HANDLE_BYTES 64
+int rof_shared_alloc(int64_t bytes, void** ptr, unsigned char* handle);
+int rof_shared_open(const unsigned char* handle, void** ptr);
+int rof_shared_close(void* ptr);
+int rof_shared_free(void* ptr);
 
 /* Reads and clears the plan's device status word: non-zero when a bounded wait inside a kernel
  * of an earlier pass ran out (that pass's output is incomplete).  rof_aggregate() checks it on

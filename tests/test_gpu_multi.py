@@ -80,6 +80,21 @@ def _worker(rank, world, port, name, q):
         for _ in range(3):
             pp.aggregate(local[:r1 - r0], dpad, mode, out5)
         torch.cuda.synchronize()
+        # the staged pipeline with the peers' blocks pulled by the copy engines out of shared buffers
+        feats_c = ShardedFeatures(n, dim, rank, world, dev, bounds=bal, shared=True)
+        feats_c.local_view().copy_(torch.from_numpy(x[b0:b1]).to(dev))
+        out7 = torch.empty((b1 - b0, dim), device=dev)
+        pipe7 = PipelinedAggregator(plan_b, feats_c, transport="copy", pieces=2)
+        for it in range(3):
+            if it == 2:        # new rows in the own block between passes: peers must see them, not a mix
+                feats_c.local_view().copy_(torch.from_numpy(x[b0:b1]).to(dev))
+            else:
+                feats_c.local_view().copy_(torch.from_numpy(x[b0:b1] * (it + 2.0)).to(dev))
+            pipe7.aggregate(None, deg, mode, out7)
+        torch.cuda.synchronize()
+        pipe7.windows.close()
+        dist.barrier()
+        feats_c.shared.close()
         # destinations x sources grid: all-gather inside the column group, reduce-scatter of partial
         # rows inside the destination group (2 GPUs: a 1 x 2 grid, reduce-scatter only; 4: 2 x 2)
         from artifact_b200.grid import GridLayout, GridPipeline
@@ -93,7 +108,7 @@ def _worker(rank, world, port, name, q):
             gp.aggregate(local[:r1 - r0], deg[r0:r1], mode, out6)
         torch.cuda.synchronize()
         res[mode] = (a, out.cpu().numpy(), out2.cpu().numpy(), (b0, out3.cpu().numpy()), out4.cpu().numpy(),
-                     out5.cpu().numpy(), out6.cpu().numpy())
+                     out5.cpu().numpy(), out6.cpu().numpy(), (b0, out7.cpu().numpy()))
     gathered = [None] * world
     dist.all_gather_object(gathered, (r0, res))
     if rank == 0:
@@ -135,6 +150,8 @@ def test_sharded_and_pipelined_match_oracle(name):
         assert_close(piped2, want, what=f"pipelined, two half stages, {mode}")
         piped5 = np.concatenate([r[mode][5] for _, r in sorted(gathered, key=lambda t: t[0])])
         assert_close(piped5, want, what=f"piece-major pipeline, {mode}")
+        pulled = np.concatenate([o for _, o in sorted((r[mode][7] for _, r in gathered), key=lambda t: t[0])])
+        assert_close(pulled, want, what=f"pipelined, copy-engine transport, {mode}")
         grid = np.concatenate([r[mode][6] for _, r in sorted(gathered, key=lambda t: t[0])])
         assert_close(grid, want, what=f"destination x source grid, {mode}")
         piped4 = np.concatenate([r[mode][4] for _, r in sorted(gathered, key=lambda t: t[0])])

@@ -212,3 +212,35 @@ def test_grid_pipeline_ranks_emulated_on_one_gpu(world, cols, chunks):
             out = torch.empty((r1 - r0, dim), device=DEV)
             scale_rows(mine[:r1 - r0, :dim], deg[r0:r1], op, out=out)
             assert_close(out.cpu().numpy(), want[r0:r1], what=f"grid {world // cols}x{cols}, rank {gl.rank}, {mode}")
+
+
+@pytest.mark.gpu
+def test_shared_store_and_copy_entry_point():
+    """the buffer peers map for copy-engine transfers: its own allocation wrapped (not copied) by a
+    torch tensor, usable as a feature matrix, and rof_copy_async between two such buffers"""
+    import ctypes
+    from artifact_b200 import _native
+    from artifact_b200.sharding import ShardedFeatures, SharedStore
+    a, b = SharedStore(100, 12, DEV), SharedStore(100, 12, DEV)
+    assert a.tensor.data_ptr() == a.ptr and a.tensor.shape == (100, 12) and len(a.handle) == 64
+    assert float(a.tensor.abs().sum()) == 0.0
+    a.tensor.copy_(torch.arange(1200, device=DEV, dtype=torch.float32).view(100, 12))
+    st = torch.cuda.current_stream()
+    _native.check(_native.cuda().rof_copy_async(ctypes.c_void_p(b.ptr + 10 * 48), ctypes.c_void_p(a.ptr + 20 * 48), 30 * 48,
+                                                ctypes.c_void_p(st.cuda_stream)))
+    torch.cuda.synchronize()
+    assert torch.equal(b.tensor[10:40], a.tensor[20:50]) and float(b.tensor[:10].abs().sum()) == 0.0
+    a.close(); b.close()
+    # a feature buffer on a shared store behaves like any other
+    g = load_golden("c2_n640_ps2")
+    n, L, dim = g["N"], g["layouts"], 10
+    f = ShardedFeatures(n, dim, 0, 1, DEV, shared=True)
+    x = np.random.default_rng(3).standard_normal((n, dim)).astype(np.float32)
+    f.full.copy_(torch.from_numpy(x))
+    plan = AggregationPlan.from_v2(n, *[torch.from_numpy(np.ascontiguousarray(v, dtype=np.int32)).to(DEV) for v in layout_args(L, "v2")])
+    got = plan.aggregate(f.full[:n], None, "sum")
+    want = rof_oracle.aggregate_v2(x, L["uniqpart_column_index"], g["degrees"], L["uniqpart_pointers"],
+                                   L["part2Node_ptr"], L["part2Node_col"], "sum", True)
+    assert_close(got.cpu().numpy(), want, what="features on a shared store")
+    del got, plan
+    f.shared.close()
