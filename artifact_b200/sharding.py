@@ -279,16 +279,26 @@ class PeerWindows:
         everyone = [None] * world
         dist.all_gather_object(everyone, (store.handle, store.bytes), group=group)
         self.base = {}
-        with torch.cuda.device(self.device):
-            for r, (handle, nbytes) in enumerate(everyone):
-                if r == rank:
-                    continue
-                if nbytes != store.bytes:
-                    raise RuntimeError(f"rank {r}'s buffer has another size than this rank's")
-                ptr = ctypes.c_void_p()
-                buf = (ctypes.c_ubyte * 64).from_buffer_copy(handle)
-                _native.check(_native.cuda().rof_shared_open(buf, ctypes.byref(ptr)))
-                self.base[r] = ptr.value
+        err = None
+        try:
+            with torch.cuda.device(self.device):
+                for r, (handle, nbytes) in enumerate(everyone):
+                    if r == rank:
+                        continue
+                    if nbytes != store.bytes:
+                        raise RuntimeError(f"rank {r}'s buffer has another size than this rank's")
+                    ptr = ctypes.c_void_p()
+                    buf = (ctypes.c_ubyte * 64).from_buffer_copy(handle)
+                    _native.check(_native.cuda().rof_shared_open(buf, ctypes.byref(ptr)))
+                    self.base[r] = ptr.value
+        except Exception as ex:                   # every rank must learn of it: they fail together below
+            err = repr(ex)
+        status = [None] * world
+        dist.all_gather_object(status, err, group=group)
+        bad = [(r, e) for r, e in enumerate(status) if e]
+        if bad:
+            self.close()
+            raise RuntimeError(f"rank {bad[0][0]} could not map its peers' buffers: {bad[0][1]}")
 
     def pull(self, dst, peer, byte_offset, stream):
         """`dst` (contiguous rows of the local buffer) <- the bytes at `byte_offset` of rank `peer`'s

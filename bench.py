@@ -420,21 +420,48 @@ class Job:
                                "source_tiles_per_chunk": px.tiles}
         else:
             bounds = self.blocks if kind == "stages" else None
-            transport = getattr(ns, "transport", "nccl") if kind == "stages" else "nccl"
-            self.feat_x = ShardedFeatures(n, D, rank, world, dev, bounds=bounds, shared=transport == "copy")
-            self.feat_g = ShardedFeatures(n, D, rank, world, dev, bounds=bounds, shared=transport == "copy")
+            want = getattr(ns, "transport", "auto") if kind == "stages" else "nccl"
+            sched = [[int(k) for k in st.split(",")] for st in ns.schedule.split("|")] if getattr(ns, "schedule", "") else None
+
+            def build(transport):
+                fx = ShardedFeatures(n, D, rank, world, dev, bounds=bounds, shared=transport == "copy")
+                fg = ShardedFeatures(n, D, rank, world, dev, bounds=bounds, shared=transport == "copy")
+                if kind != "stages":
+                    return fx, fg, None, None
+                px = PipelinedAggregator(self.plan, fx, schedule=sched, pieces=getattr(ns, "pieces", 0) or None,
+                                         transport=transport)
+                return fx, fg, px, PipelinedAggregator(self.plan, fg, like=px, transport=transport)
+
+            transport, why = ("copy" if want in ("auto", "copy") else "nccl"), None
+            if transport == "copy":
+                # mapping the peers' buffers can fail where interprocess handles are not allowed; every rank
+                # then falls back to NCCL send/receive together (the constructors' collectives have completed
+                # on every rank by the time one of them raises)
+                built = None
+                try:
+                    built = build("copy")
+                except Exception as ex:          # noqa: BLE001 - reported in the JSON line
+                    why = repr(ex)[:200]
+                import torch.distributed as dist
+                flag = torch.tensor([1 if built is not None else 0], device=dev)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                if int(flag.item()) == 0:
+                    if want == "copy":
+                        raise RuntimeError(f"--transport copy: a rank could not map its peers' buffers ({why})")
+                    built, transport = None, "nccl"
+            if transport == "nccl":
+                built = build("nccl")
+            self.feat_x, self.feat_g, px, pg = built
             self.feat_x.full.normal_(generator=gen); self.feat_g.full.normal_(generator=gen)
             if kind == "stages":
-                sched = [[int(k) for k in st.split(",")] for st in ns.schedule.split("|")] if ns.schedule else None
-                px = PipelinedAggregator(self.plan, self.feat_x, schedule=sched, pieces=getattr(ns, "pieces", 0) or None,
-                                         transport=transport)
-                self.pipes = {id(self.feat_x): px,
-                              id(self.feat_g): PipelinedAggregator(self.plan, self.feat_g, like=px, transport=transport)}
+                self.pipes = {id(self.feat_x): px, id(self.feat_g): pg}
                 self.stage_info = {"kind": "stages of source blocks, " + ("grouped send/receive" if transport == "nccl" else
                                                                          "peers' blocks pulled by the copy engines"),
-                                   "peer_groups": px.schedule,
+                                   "transport": transport, "peer_groups": px.schedule,
                                    "pieces_per_group": px.pieces, "transfer_stages": len(px.transfers),
                                    "compute_stages": len(px.stage_plans)}
+                if why and transport == "nccl":
+                    self.stage_info["copy_transport_unavailable"] = why
             else:
                 self.tiles = self.plan.auto_tiles(D) if ns.tiles == "auto" else int(ns.tiles)
         self.t_plan = time.time() - t0
@@ -706,6 +733,14 @@ class Job:
                         "are summed over the ranks; the graph plan stays resident like upstream's inputInfo tensors"}
 
     def release(self):
+        # buffers that peers have mapped: every rank unmaps first, then the owners free
+        windows = [p.windows for p in (self.pipes or {}).values() if getattr(p, "transport", "") == "copy"]
+        if windows:
+            import torch.distributed as dist
+            self.torch.cuda.synchronize()
+            for w in windows:
+                w.close()
+            dist.barrier()
         for k in ("plan", "plain", "pipes", "feat_x", "feat_g", "full_x", "full_g", "out_f", "out_b", "deg", "L", "g",
                   "grid_plans"):
             setattr(self, k, None)
@@ -811,8 +846,9 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="shrink the graph (tests / profiling only)")
     ap.add_argument("--no-pipeline", dest="pipeline", action="store_false",
                     help="N > 1: one all-gather, then the aggregation (no overlap)")
-    ap.add_argument("--transport", default="nccl", choices=["nccl", "copy"],
-                    help="N > 1, stage pipeline: grouped NCCL send/receive, or copy engines pulling from the peers' buffers")
+    ap.add_argument("--transport", default="auto", choices=["auto", "nccl", "copy"],
+                    help="N > 1, stage pipeline: copy engines pulling from the peers' buffers (auto: with NCCL send/receive "
+                         "as the fall-back where the buffers cannot be mapped), or grouped NCCL send/receive")
     ap.add_argument("--grid-cols", type=int, default=0, help="N > 1, grid pipeline: columns of the grid (0: by world size)")
     ap.add_argument("--pipeline-kind", default="auto", choices=["auto", "pieces", "columns", "stages", "grid"],
                     help="N > 1: exchange the features piece-major (one all-gather per L2-sized piece of every block), "
