@@ -11,9 +11,10 @@ seeded synthetic graph of the workload, through the reuse plan built from the RO
 `value` is edges/s with the ORIGINAL edge count (reuse shows up as more edges per second),
 inputs resident in HBM; `e2e` is the same step through the public API with pinned-host inputs
 and outputs, copies inside the timed region.  With N > 1 the destination rows are cut into N
-blocks of equal work; every pass moves the feature blocks between the ranks over NCCL (staged
-send/receive groups overlapped with the per-stage aggregation, or one all-gather with
---no-pipeline) and the same total work is divided (strong scaling).  On one GPU a feature matrix
+blocks of equal work; every pass moves the feature blocks between the ranks over NVLink in stages
+that overlap the per-stage aggregation (by default the copy engines pull the peers' blocks out of
+shared buffers; --transport nccl, --pipeline-kind and --no-pipeline select the other paths) and the
+same total work is divided (strong scaling).  On one GPU a feature matrix
 larger than L2 is walked in source tiles (--tiles).  After the timed region every rank
 recomputes a sample of its output rows in fp64 on the host (`check`); a failed check makes the
 run exit non-zero.  Prints ONE JSON line on rank 0.
@@ -292,20 +293,11 @@ def prepare_workload(args, rank, world):
 
 
 def pipeline_kind(args, world, g):
-    """--pipeline-kind auto: two ranks -> stages (the own block is half of the matrix and needs no transfer);
-    more ranks -> the stages' point-to-point transfers fall behind the collectives: piece-major where the rows
-    are long enough to be cut into pieces, else column chunks (8 B200s, 50 entries per row, D=256: 10.4 ms per
-    step in 4 column chunks, 10.9 ms with one all-gather and the whole plan, 11.9 ms in stages)."""
+    """--pipeline-kind auto: the stage pipeline, whose transfers the copy engines carry (4 B200s: 3.17 ms per
+    step against 3.62 ms with piece-major all-gathers on the 114.6M-edge graph, 11.97 against 12.55 and 0.81
+    against 1.09 on the other two configurations; 2 B200s: 16.8 against 19.8 ms where the gather is HBM-bound)."""
     kind = getattr(args, "pipeline_kind", "auto")
-    if kind != "auto":
-        return kind
-    if world <= 2:
-        return "stages"
-    if getattr(args, "pieces", 0):
-        return "pieces"
-    from artifact_b200.sharding import PieceMajorPipeline
-    P = PieceMajorPipeline.default_pieces(g.num_nodes, args.dim, world, g.num_edges / max(g.num_nodes, 1))
-    return "pieces" if P > 1 else "columns"
+    return "stages" if kind == "auto" else kind
 
 
 def workload_config(args, g, ratios):
@@ -318,7 +310,8 @@ def workload_config(args, g, ratios):
                                        "with the aggregation of the piece before",
                              "columns": "features exchanged in column chunks, one all-gather each, overlapped with the "
                                         "chunks' aggregation",
-                             "stages": "blocks of equal work, staged send/receive overlapped with per-stage aggregation",
+                             "stages": "blocks of equal work, peers' blocks fetched in stages (copy engines, or NCCL "
+                                       "send/receive) overlapped with per-stage aggregation",
                              "grid": "destination x source grid: all-gather inside the column group, partial rows "
                                      "reduce-scattered inside the destination group chunk by chunk"
                              }[pipeline_kind(args, args.gpus, g)]
