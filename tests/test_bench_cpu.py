@@ -61,3 +61,26 @@ def test_two_ranks_share_one_search_through_the_cache(tmp_path):
             assert p.exitcode == 0
         assert got[0][1:] == got[1][1:] and got[0][3] > 0
     assert len(list(tmp_path.glob("*.npz"))) == 1
+
+
+def test_default_pipeline_and_its_description():
+    """N > 1 defaults: the stage pipeline at every GPU count; an explicit kind passes through; the
+    configuration text names the path that runs"""
+    import argparse
+    sys.path.insert(0, ROOT)
+    import bench
+
+    class G:
+        num_nodes, num_edges = 1000, 50000
+
+    auto = argparse.Namespace(pipeline_kind="auto", pieces=0, dim=64, gpus=8, workload="c2", mode="sum", part_size=2,
+                              scale=1.0, tiles="auto", pipeline=True)
+    for world in (2, 4, 8):
+        assert bench.pipeline_kind(auto, world, G) == "stages"
+    for kind in ("pieces", "columns", "stages", "grid"):
+        ns = argparse.Namespace(**dict(vars(auto), pipeline_kind=kind))
+        assert bench.pipeline_kind(ns, 8, G) == kind
+        assert "row-block x8" in bench.workload_config(ns, G, None)["parallelism"]
+    assert "copy engines" in bench.workload_config(auto, G, None)["parallelism"]
+    one = argparse.Namespace(**dict(vars(auto), gpus=1))
+    assert bench.workload_config(one, G, None)["parallelism"] == "single GPU"
