@@ -26,7 +26,7 @@ import torch
 import torch.distributed as dist
 
 from .plan import AggregationPlan, padded_width, scale_rows
-from .sharding import row_blocks
+from .sharding import PeerWindows, SharedStore, row_blocks
 
 
 class GridLayout:
@@ -132,16 +132,39 @@ class GridPipeline:
                 dst = g
         return col, dst
 
-    def __init__(self, layout, plans, dim, device, groups=None, like=None):
+    def __init__(self, layout, plans, dim, device, groups=None, like=None, transport="nccl"):
+        """transport "nccl": all_gather_into_tensor and reduce_scatter_tensor.  transport "copy"
+        (collective constructor): the source and the partial buffers are shared stores that the
+        peers map; a rank pulls the other slots of its column group and, chunk by chunk, the partial
+        rows of its own block from the other ranks of its destination group with asynchronous copies
+        (copy engines), and adds them itself.  One-float all-reduces on the transfer stream tell the
+        ranks when a slot or a chunk may be read and when the buffers may be written again."""
         L = layout
         self.layout, self.plans, self.dim, self.device = L, plans, int(dim), torch.device(device)
         ld = padded_width(dim)
-        self._src = torch.zeros((L.m, ld), device=device)           # rows [0, r*blk): the column group's features
+        self.groups = groups if like is None else like.groups
+        self.transport = transport if (self.groups is not None and L.world > 1) else "nccl"
+        if self.transport not in ("nccl", "copy"):
+            raise ValueError("transport must be 'nccl' or 'copy'")
+        self.src_win = self.part_win = None
+        if self.transport == "copy":
+            self.src_store = SharedStore(L.m, ld, device)
+            self.part_store = SharedStore(L.dst_rows, ld, device)
+            self._src, self._partial = self.src_store.tensor, self.part_store.tensor
+            if L.r > 1:
+                self.src_win = PeerWindows(self.src_store, L.i, L.r, self.groups[0])
+            if L.c > 1:
+                self.part_win = PeerWindows(self.part_store, L.j, L.c, self.groups[1])
+            # the partial rows of this rank's block as the other ranks of the destination group hold them
+            self._incoming = torch.zeros((max(L.c - 1, 1), L.q * L.cb, ld), device=device)
+            self._token = torch.zeros(1, device=device)
+            self.released = torch.cuda.Event()
+        else:
+            self._src = torch.zeros((L.m, ld), device=device)       # rows [0, r*blk): the column group's features
+            self._partial = torch.zeros((L.dst_rows, ld), device=device)
         self.sources = self._src[:, :dim]
-        self._partial = torch.zeros((L.dst_rows, ld), device=device)
         self.partial = self._partial[:, :dim]
         self._reduced = torch.zeros((L.q * L.cb, ld), device=device)
-        self.groups = groups if like is None else like.groups
         self.comm = torch.cuda.Stream(device, priority=-1)
         self.ready = torch.cuda.Event()
         self.gathered = torch.cuda.Event()
@@ -164,7 +187,14 @@ class GridPipeline:
             self.ready.record(cur)
             with torch.cuda.stream(self.comm):
                 self.comm.wait_event(self.ready)
-                dist.all_gather_into_tensor(self._src[:L.src_rows], self.own_slot(), group=self.groups[0])
+                if self.transport == "copy":
+                    dist.all_reduce(self._token, group=self.groups[0])       # every own slot of the group is written
+                    row_bytes = self._src.stride(0) * 4
+                    for ii in range(L.r):
+                        if ii != L.i:
+                            self.src_win.pull(self._src[ii * L.blk:(ii + 1) * L.blk], ii, ii * L.blk * row_bytes, self.comm)
+                else:
+                    dist.all_gather_into_tensor(self._src[:L.src_rows], self.own_slot(), group=self.groups[0])
                 self.gathered.record(self.comm)
             cur.wait_event(self.gathered)
 
@@ -182,11 +212,35 @@ class GridPipeline:
         self.done[q].record(cur)
         with torch.cuda.stream(self.comm):
             self.comm.wait_event(self.done[q])
-            if L.c > 1:
+            if self.transport == "copy":
+                if L.c > 1:
+                    dist.all_reduce(self._token, group=self.groups[1])       # chunk q is complete on every rank of the group
+                    row_bytes = self._partial.stride(0) * 4
+                    k = 0
+                    for jj in range(L.c):
+                        if jj != L.j:
+                            self.part_win.pull(self._incoming[k][q * L.cb:(q + 1) * L.cb], jj,
+                                               (a + L.j * L.cb) * row_bytes, self.comm)
+                            k += 1
+            elif L.c > 1:
                 dist.reduce_scatter_tensor(out, self._partial[a:b], group=self.groups[1])
             else:
                 out.copy_(self._partial[a:b])
             self.reduced[q].record(self.comm)
+
+    def _add_pulled(self):
+        """finished sums of this rank's block = its own partial rows + the ones pulled from the peers"""
+        L = self.layout
+        ld = self._partial.shape[1]
+        own = self._partial.view(L.q, L.c, L.cb, ld)[:, L.j]
+        acc = self._reduced.view(L.q, L.cb, ld)
+        if L.c > 1:
+            torch.add(own, self._incoming[0].view(L.q, L.cb, ld), out=acc)
+            for k in range(1, L.c - 1):
+                acc.add_(self._incoming[k].view(L.q, L.cb, ld))
+            return L.c - 1
+        acc.copy_(own)
+        return 1
 
     def aggregate(self, x_local, degrees_local, mode, out, transfers=True, kernels=True):
         """x_local: this rank's [rows, dim] features (None: the own slot is already filled);
@@ -208,13 +262,27 @@ class GridPipeline:
         if transfers:
             for ev in self.reduced:
                 cur.wait_event(ev)
+            if self.transport == "copy":
+                with torch.cuda.stream(self.comm):       # every rank has pulled what it needs: buffers may be rewritten
+                    dist.all_reduce(self._token)
+                    self.released.record(self.comm)
         if kernels:
+            if self.transport == "copy":
+                launches += self._add_pulled()
             rows = out.size(0)
             op = {"sum": "copy", "mean": "reciprocal", "gcn": "rsqrt"}[mode]
             scale_rows(self._reduced[:rows, :self.dim], degrees_local, op, out=out)
             launches += 1
+        if transfers and self.transport == "copy":
+            cur.wait_event(self.released)
         self.launches = launches
         return out
+
+    def close_windows(self):
+        """unmap the peers' buffers (every rank, before any owner frees its stores)"""
+        for w in (self.src_win, self.part_win):
+            if w is not None:
+                w.close()
 
     def transfer_only(self):
         """the pass's collectives without its kernels (timing breakdown)"""

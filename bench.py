@@ -394,12 +394,13 @@ class Job:
         elif kind == "grid":
             self.full_x = torch.empty((n, D), device=dev).normal_(generator=gen)
             self.full_g = torch.empty((n, D), device=dev).normal_(generator=gen)
-            px = GridPipeline(self.grid, self.grid_plans, D, dev, groups=self.grid_groups)
-            pg = GridPipeline(self.grid, self.grid_plans, D, dev, like=px)
+            tr = "nccl" if getattr(ns, "transport", "auto") == "nccl" else "copy"
+            px = GridPipeline(self.grid, self.grid_plans, D, dev, groups=self.grid_groups, transport=tr)
+            pg = GridPipeline(self.grid, self.grid_plans, D, dev, like=px, transport=tr)
             self.feat_x, self.feat_g = px, pg
             self.pipes = {id(px): px, id(pg): pg}
             self.deg_local = self.deg[self.r0:self.r1].contiguous()
-            self.stage_info = {"kind": "destination x source grid", "grid": [self.grid.r, self.grid.c],
+            self.stage_info = {"kind": "destination x source grid", "transport": px.transport, "grid": [self.grid.r, self.grid.c],
                                "destination_chunks": self.grid.q, "rows_per_rank_and_chunk": self.grid.cb,
                                "received_rows_fraction": round((self.grid.r + self.grid.c - 2) / world, 4)}
         elif kind == "columns":
@@ -727,12 +728,12 @@ class Job:
 
     def release(self):
         # buffers that peers have mapped: every rank unmaps first, then the owners free
-        windows = [p.windows for p in (self.pipes or {}).values() if getattr(p, "transport", "") == "copy"]
-        if windows:
+        mapped = [p for p in (self.pipes or {}).values() if getattr(p, "transport", "") == "copy"]
+        if mapped:
             import torch.distributed as dist
             self.torch.cuda.synchronize()
-            for w in windows:
-                w.close()
+            for p in mapped:
+                p.close_windows() if hasattr(p, "close_windows") else p.windows.close()
             dist.barrier()
         for k in ("plan", "plain", "pipes", "feat_x", "feat_g", "full_x", "full_g", "out_f", "out_b", "deg", "L", "g",
                   "grid_plans"):

@@ -107,8 +107,17 @@ def _worker(rank, world, port, name, q):
         for _ in range(3):
             gp.aggregate(local[:r1 - r0], deg[r0:r1], mode, out6)
         torch.cuda.synchronize()
+        # the same grid with every transfer a copy-engine pull out of the peers' shared buffers
+        gc = GridPipeline(gl, grid_plans, dim, dev, groups=grid_groups, transport="copy")
+        out8 = torch.empty((r1 - r0, dim), device=dev)
+        for it in range(3):
+            gc.aggregate(local[:r1 - r0] * (1.0 if it == 2 else it + 2.0), deg[r0:r1], mode, out8)
+        torch.cuda.synchronize()
+        gc.close_windows()
+        dist.barrier()
+        gc.src_store.close(); gc.part_store.close()
         res[mode] = (a, out.cpu().numpy(), out2.cpu().numpy(), (b0, out3.cpu().numpy()), out4.cpu().numpy(),
-                     out5.cpu().numpy(), out6.cpu().numpy(), (b0, out7.cpu().numpy()))
+                     out5.cpu().numpy(), out6.cpu().numpy(), (b0, out7.cpu().numpy()), out8.cpu().numpy())
     gathered = [None] * world
     dist.all_gather_object(gathered, (r0, res))
     if rank == 0:
@@ -152,6 +161,8 @@ def test_sharded_and_pipelined_match_oracle(name):
         assert_close(piped5, want, what=f"piece-major pipeline, {mode}")
         pulled = np.concatenate([o for _, o in sorted((r[mode][7] for _, r in gathered), key=lambda t: t[0])])
         assert_close(pulled, want, what=f"pipelined, copy-engine transport, {mode}")
+        grid_c = np.concatenate([r[mode][8] for _, r in sorted(gathered, key=lambda t: t[0])])
+        assert_close(grid_c, want, what=f"destination x source grid, copy-engine transport, {mode}")
         grid = np.concatenate([r[mode][6] for _, r in sorted(gathered, key=lambda t: t[0])])
         assert_close(grid, want, what=f"destination x source grid, {mode}")
         piped4 = np.concatenate([r[mode][4] for _, r in sorted(gathered, key=lambda t: t[0])])
