@@ -70,6 +70,11 @@ def test_argument_checks_of_the_auxiliary_entry_points():
     assert lib.rof_probe_read(ctypes.c_void_p(p.value + 4), 1024, 1, p, None) == 1   # not 16-byte aligned
     assert lib.rof_copy_async(None, p, 16, None) == 1 and lib.rof_copy_async(p, None, 16, None) == 1
     assert lib.rof_copy_async(p, p, -1, None) == 1 and lib.rof_copy_async(None, None, 0, None) == 0
+    out_ptr = ctypes.c_void_p()
+    assert lib.rof_shared_alloc(0, ctypes.byref(out_ptr), p) == 1 and lib.rof_shared_alloc(64, None, p) == 1
+    assert lib.rof_shared_alloc(64, ctypes.byref(out_ptr), None) == 1
+    assert lib.rof_shared_open(None, ctypes.byref(out_ptr)) == 1 and lib.rof_shared_open(p, None) == 1
+    assert lib.rof_shared_close(None) == 0 and lib.rof_shared_free(None) == 0
     assert lib.rof_plan_take_status(None) == 0
     assert lib.rof_plan_export_tiles(None, None, None, None, None) == 1
     handles = (ctypes.c_void_p * 2)()
