@@ -48,6 +48,7 @@ CACHE_VERSION = 2          # bump when the graph generators or the search change
 NCU_DRAM_BYTES_PER_PASS = {
     "c2:D256:sum": 3.35e9,     # 4 source tiles; two captured: 0.71 and 0.96 GB (untiled first version: 25.0 GB)
     "c2:D256:gcn": 3.9e9,      # two of four tiles captured: 0.84 and 1.11 GB
+    "c2:D128:sum": 1.5e9,      # one of two tiles captured: 0.76 GB
     "c2:D602:sum": 17.2e9,     # two of eight tiles captured: 1.80 and 2.49 GB
     "c5:D64:sum": 2.04e9,      # tile kernel
 }
