@@ -16,7 +16,9 @@ Received per pass: (r + c - 2)/R of N*D — 0.5 at 2 x 4 against 0.875 for row b
 partial rows are produced in Q chunks of destinations, laid out so that each chunk is one
 reduce_scatter_tensor, and chunk q travels while chunk q+1 is gathered.  GCN rows travel pre-scaled
 by rsqrt(deg) of the source; the kernels run in sum mode and step 4 applies rsqrt(deg) (or 1/deg) of
-the destination.  Upstream has no multi-GPU path (ROF_evaluation/ROF_main.py runs one process).
+the destination.  Steps 1 and 3 run either as NCCL collectives or as asynchronous copies out of the
+peers' shared buffers (copy engines) followed by a local add (GridPipeline's `transport`).  Upstream
+has no multi-GPU path (ROF_evaluation/ROF_main.py runs one process).
 
 Reuse groups are not used here: a group's sources may lie in different column groups.  The plans are
 built from the destination CSR (the `SAG` / `GNNA` layout of upstream, reuse_conv.cpp:132-205).
